@@ -1,0 +1,300 @@
+"""Generate the golden fixtures in this folder from the reference implementation.
+
+Run in a container where the reference checkout is importable:
+
+    python tests/golden/make_goldens.py --reference /path/to/lingbot-map
+
+It imports the reference's own Python code on CPU (the FlashInfer wrapper class is replaced by a
+no-op stub because its constructor needs a GPU; all bookkeeping and the fp32 gather+SDPA path of the
+cache manager are the reference's own), drives it with seeded inputs (tests/golden/seeded.py) and
+stores only the outputs.  The tests regenerate the inputs from the same seeds.
+"""
+import argparse
+import gzip
+import json
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+import seeded  # noqa: E402
+
+
+def _import_reference(path):
+    sys.dont_write_bytecode = True
+    sys.path.insert(0, path)
+    import flashinfer
+
+    class _Stub:
+        def __init__(self, *a, **k):
+            pass
+    flashinfer.BatchPrefillWithPagedKVCacheWrapper = _Stub
+
+
+def _snap(m, b=0):
+    return {"visible": [int(x) for x in m.build_visible_page_table(b)],
+            "last_page_len": int(m.compute_last_page_len(b)),
+            "stats": m.get_cache_stats(b),
+            "n_scale": len(m.scale_patch_pages[b]), "n_window": len(m.live_window_patch_pages[b]),
+            "free_patch": [int(x) for x in m.free_patch_pages[b]],
+            "free_special": [int(x) for x in m.free_special_pages[b]]}
+
+
+def manager_traces():
+    import torch
+    from lingbot_map.layers.flashinfer_cache import FlashInferKVCacheManager
+
+    def make(tpf, scale, window, max_total, heads=1, nb=1):
+        return FlashInferKVCacheManager(
+            num_blocks=nb, max_num_frames=scale + window + 16, tokens_per_frame=tpf, num_heads=heads,
+            head_dim=8, dtype=torch.float32, device=torch.device("cpu"), num_special_tokens=6,
+            scale_frames=scale, sliding_window=window, max_total_frames=max_total, force_fp32=True)
+
+    cases = []
+
+    def geometry(m, tpf, scale, window, max_total):
+        return {"tokens_per_frame": tpf, "scale_frames": scale, "sliding_window": window,
+                "max_total_frames": max_total, "page_size": m.page_size,
+                "max_patch_pages": m.max_patch_pages, "max_num_pages": m.max_num_pages}
+
+    def run(name, tpf, scale, window, max_total, ops, snap_at=None):
+        m = make(tpf, scale, window, max_total)
+        k = torch.zeros(tpf, 1, 8)
+        snaps = []
+        for i, op in enumerate(ops):
+            if op == "append":
+                m.append_frame(0, k, k)
+            elif op == "evict":
+                m.evict_frames(0, scale, window)
+            elif op == "defer_on":
+                m._defer_eviction = True
+            elif op == "defer_off":
+                m._defer_eviction = False
+            elif op == "exec_deferred":
+                m.execute_deferred_eviction(0, scale, window)
+            elif op == "rollback":
+                m.rollback_last_frame(0)
+            elif op == "reset":
+                m.reset()
+            else:
+                raise ValueError(op)
+            if snap_at is None or i in snap_at:
+                s = _snap(m)
+                s["op_index"] = i
+                snaps.append(s)
+        cases.append({"name": name, "geometry": geometry(m, tpf, scale, window, max_total),
+                      "ops": ops, "snapshots": snaps})
+
+    # the reference's own _sanity_check geometry (flashinfer_cache.py:577-631): 100 frames
+    run("sanity_262", 262, 8, 64, 200, ["append", "evict"] * 100)
+    # small geometry with a non-keyframe emulation at the end (block.py:256-263)
+    run("small_26", 26, 2, 3, 40,
+        ["append", "evict"] * 9 + ["defer_on", "append", "evict", "rollback", "defer_off"]
+        + ["append", "evict"] * 3 + ["reset"] + ["append", "evict"] * 4)
+    # production geometry 378x518: 1005 tokens, page 999, 400 keyframes, sparse snapshots
+    frames = [1, 8, 9, 72, 73, 74, 166, 167, 168, 333, 334, 400]
+    run("full_1005", 1005, 8, 64, 1124, ["append", "evict"] * 400,
+        snap_at={2 * f - 1 for f in frames})
+    # keyframe interval 3 at the production geometry: non-keyframes temp-append and roll back
+    ops = ["append", "evict"] * 8
+    for i in range(8, 260):
+        if (i - 8) % 3 == 0:
+            ops += ["append", "evict"]
+        else:
+            ops += ["defer_on", "append", "evict", "rollback", "defer_off"]
+    run("full_1005_kf3", 1005, 8, 64, 1124, ops, snap_at=set(range(len(ops) - 40, len(ops))) | set(range(0, 60)))
+    # random op sequences, incl. flow-style deferred eviction (gct_stream_window.py:362-419)
+    for seed in range(4):
+        rs = np.random.RandomState(100 + seed)
+        tpf = [26, 11, 38, 70][seed]
+        scale, window = [(2, 3), (1, 2), (3, 5), (0, 4)][seed]
+        ops, depth, deferred, pending = [], 0, False, False
+        for _ in range(220):
+            r = rs.rand()
+            if deferred:
+                if not pending:
+                    ops += ["append", "evict"]
+                    depth += 1
+                    pending = True
+                elif r < 0.5:
+                    ops += ["rollback", "defer_off"]
+                    depth -= 1
+                    deferred = pending = False
+                else:
+                    ops += ["exec_deferred", "defer_off"]
+                    deferred = pending = False
+            elif r < 0.55:
+                ops += ["append", "evict"]
+                depth += 1
+            elif r < 0.85:
+                ops += ["defer_on"]
+                deferred = True
+            elif r < 0.97 and depth > 0 and depth <= scale:
+                # rollback right after an append in the scale phase (no eviction happened yet)
+                ops += ["append", "rollback"]
+            elif r >= 0.97:
+                ops += ["reset"]
+                depth = 0
+        if deferred:
+            ops += ["defer_off"]
+        run(f"random_{seed}", tpf, scale, window, 150, ops)
+    with gzip.open(os.path.join(HERE, "manager_traces.json.gz"), "wt") as f:
+        json.dump(cases, f, separators=(",", ":"))
+    print("manager_traces.json.gz:", len(cases), "cases")
+
+
+def paged_attention_values():
+    """Reference manager, fp32 gather+SDPA path (flashinfer_cache.py:372-383), seeded K/V/Q."""
+    import torch
+    from lingbot_map.layers.flashinfer_cache import FlashInferKVCacheManager
+    out = {}
+    specs = {  # name: (tokens_per_frame, heads, scale, window, frames, max_total, value scale, frames stored)
+        "p20": (26, 4, 2, 3, 9, 40, 1.0, None),
+        "p150": (156, 1, 1, 2, 30, 60, 1.0, {0, 1, 5, 24, 25, 29}),
+        "p300": (306, 1, 2, 2, 12, 40, 0.125, {0, 3, 11}),
+    }
+    meta = {}
+    for name, (tpf, H, scale, window, frames, max_total, vs, keep) in specs.items():
+        m = FlashInferKVCacheManager(
+            num_blocks=1, max_num_frames=scale + window + 16, tokens_per_frame=tpf, num_heads=H, head_dim=64,
+            dtype=torch.float32, device=torch.device("cpu"), scale_frames=scale, sliding_window=window,
+            max_total_frames=max_total, force_fp32=True)
+        for t in range(frames):
+            k = torch.from_numpy(seeded.randn(1000 + t, tpf, H, 64, scale=vs))
+            v = torch.from_numpy(seeded.randn(2000 + t, tpf, H, 64, scale=vs))
+            q = torch.from_numpy(seeded.randn(3000 + t, tpf, H, 64, scale=vs))
+            m.append_frame(0, k, v)
+            m.evict_frames(0, scale, window)
+            if keep is None or t in keep:
+                out[f"{name}_out_{t}"] = m.compute_attention(0, q).numpy()
+        # one non-keyframe: deferred eviction + temporary append + attention + rollback
+        k = torch.from_numpy(seeded.randn(1000 + frames, tpf, H, 64, scale=vs))
+        v = torch.from_numpy(seeded.randn(2000 + frames, tpf, H, 64, scale=vs))
+        q = torch.from_numpy(seeded.randn(3000 + frames, tpf, H, 64, scale=vs))
+        m._defer_eviction = True
+        m.append_frame(0, k, v)
+        out[f"{name}_out_nonkf"] = m.compute_attention(0, q).numpy()
+        m.rollback_last_frame(0)
+        m._defer_eviction = False
+        out[f"{name}_visible_end"] = np.array(m.build_visible_page_table(0), np.int32)
+        meta[name] = dict(tokens_per_frame=tpf, heads=H, scale=scale, window=window, frames=frames,
+                          max_total=max_total, value_scale=vs)
+    out["meta_json"] = np.frombuffer(json.dumps(meta).encode(), dtype=np.uint8)
+    np.savez_compressed(os.path.join(HERE, "paged_attention_fp32.npz"), **out)
+    print("paged_attention_fp32.npz:", len(out), "arrays")
+
+
+def prepare_qkv_values():
+    """prepare_qkv (attention.py:402-426) with 3-D RoPE, and Attention.forward's q/k path with 2-D RoPE."""
+    import torch
+    from lingbot_map.layers.attention import FlashInferAttention, Attention
+    from lingbot_map.layers.rope import WanRotaryPosEmbed, RotaryPositionEmbedding2D, PositionGetter
+    torch.manual_seed(0)
+    out = {}
+    dim, H, pph, ppw, ns = 128, 2, 3, 4, 6
+    N = ns + pph * ppw
+    rope2d = RotaryPositionEmbedding2D(frequency=100)
+    att = FlashInferAttention(dim, num_heads=H, qk_norm=True, rope=rope2d).eval()
+    seeded.fill_module_(att, 7)
+    rope3d = WanRotaryPosEmbed(attention_head_dim=64, patch_size=(1, 14, 14), max_seq_len=64)
+    for f in (0, 5, 41):
+        x = torch.from_numpy(seeded.randn(50 + f, 1, N, dim))
+        pos3d = rope3d(ppf=1, pph=pph, ppw=ppw, patch_start_idx=ns, device=torch.device("cpu"), f_start=f, f_end=f + 1)
+        with torch.no_grad():
+            qkv = att.qkv(x)[0]                                  # [N, 3*dim]
+            q, k, v = att.prepare_qkv(x, pos=pos3d, enable_3d_rope=True)
+        out[f"rope3d_f{f}_qkv"] = qkv.numpy()
+        out[f"rope3d_f{f}_q"], out[f"rope3d_f{f}_k"], out[f"rope3d_f{f}_v"] = q.numpy(), k.numpy(), v.numpy()
+    # 2-D: positions as the aggregator builds them (base.py:416-442)
+    pos = PositionGetter()(1, pph, ppw, device=torch.device("cpu")) + 1
+    pos = torch.cat([torch.zeros(1, ns, 2, dtype=pos.dtype), pos], dim=1)
+    x = torch.from_numpy(seeded.randn(99, 1, N, dim))
+    with torch.no_grad():
+        qkv = att.qkv(x)[0]
+        q, k, v = att.prepare_qkv(x, pos=pos, enable_3d_rope=False)
+    out["rope2d_qkv"], out["rope2d_q"], out["rope2d_k"], out["rope2d_v"] = qkv.numpy(), q.numpy(), k.numpy(), v.numpy()
+    out["rope2d_pos"] = pos[0].numpy()
+    # dense frame attention incl. proj (attention.py:65-87), two frames as the batch dimension
+    fa = Attention(dim, num_heads=H, qk_norm=True, rope=rope2d).eval()
+    seeded.fill_module_(fa, 11)
+    x = torch.from_numpy(seeded.randn(123, 2, N, dim))
+    with torch.no_grad():
+        y = fa(x, pos=pos.expand(2, -1, -1))
+    out["frame_attn_out"] = y.numpy()
+    np.savez_compressed(os.path.join(HERE, "prepare_qkv_fp32.npz"), **out)
+    print("prepare_qkv_fp32.npz:", len(out), "arrays")
+
+
+def block_stream_values():
+    """FlashInferBlock (block.py:151-310) driven like AggregatorStream does: phase 1 with 2 scale frames,
+    then 8 streaming frames with keyframe interval 2; and SDPABlock with interval 1 for the dict-cache path."""
+    import torch
+    from lingbot_map.layers.block import FlashInferBlock, SDPABlock
+    from lingbot_map.layers.flashinfer_cache import FlashInferKVCacheManager
+    from lingbot_map.layers.rope import WanRotaryPosEmbed, RotaryPositionEmbedding2D
+    dim, H, pph, ppw, ns = 128, 2, 3, 4, 6
+    P = ns + pph * ppw
+    scale, window = 2, 3
+    rope3d = WanRotaryPosEmbed(attention_head_dim=64, patch_size=(1, 14, 14), max_seq_len=64)
+    dev = torch.device("cpu")
+    out = {}
+
+    def drive(block, cache, kf_interval, tag, is_paged):
+        tfp = 0
+        x = torch.from_numpy(seeded.randn(500, 1, scale * P, dim))
+        pos = rope3d(ppf=scale, pph=pph, ppw=ppw, patch_start_idx=ns, device=dev, f_start=0, f_end=scale)
+        kw = dict(num_patches=P - ns, num_special=ns, enable_3d_rope=True, kv_cache=cache, global_idx=0,
+                  num_frame_for_scale=scale, num_register_tokens=4)
+        with torch.no_grad():
+            y = block(x, pos=pos, num_frames=scale, num_frame_per_block=scale, **kw)
+        out[f"{tag}_phase1"] = y.numpy()
+        tfp += scale
+        for i in range(scale, scale + 8):
+            is_kf = kf_interval <= 1 or (i - scale) % kf_interval == 0
+            if is_paged:
+                cache._skip_append = not is_kf
+            x = torch.from_numpy(seeded.randn(500 + i, 1, P, dim))
+            pos = rope3d(ppf=1, pph=pph, ppw=ppw, patch_start_idx=ns, device=dev, f_start=tfp, f_end=tfp + 1)
+            with torch.no_grad():
+                y = block(x, pos=pos, num_frames=1, num_frame_per_block=1, **kw)
+            out[f"{tag}_frame{i}"] = y.numpy()
+            if is_kf:
+                tfp += 1
+        if is_paged:
+            cache._skip_append = False
+            out[f"{tag}_visible_end"] = np.array(cache.build_visible_page_table(0), np.int32)
+            out[f"{tag}_last_len_end"] = np.array([cache.compute_last_page_len(0)], np.int32)
+
+    common = dict(dim=dim, num_heads=H, init_values=0.01, qk_norm=True,
+                  rope=RotaryPositionEmbedding2D(frequency=100),
+                  kv_cache_sliding_window=window, kv_cache_scale_frames=scale)
+    blk = FlashInferBlock(**common).eval()
+    seeded.fill_module_(blk, 21)
+    mgr = FlashInferKVCacheManager(num_blocks=1, max_num_frames=scale + window + 16, tokens_per_frame=P, num_heads=H,
+                                   head_dim=64, dtype=torch.float32, device=dev, scale_frames=scale,
+                                   sliding_window=window, max_total_frames=40, force_fp32=True)
+    drive(blk, mgr, 2, "paged_kf2", True)
+    mgr.reset()
+    drive(blk, mgr, 1, "paged_kf1", True)
+    sblk = SDPABlock(**common).eval()
+    seeded.fill_module_(sblk, 21)
+    cache = {"k_0": None, "v_0": None, "k_0_special": None, "v_0_special": None}
+    drive(sblk, cache, 1, "sdpa_kf1", False)
+    out["param_names_json"] = np.frombuffer(json.dumps([n for n, _ in blk.named_parameters()]).encode(), dtype=np.uint8)
+    np.savez_compressed(os.path.join(HERE, "block_stream_fp32.npz"), **out)
+    print("block_stream_fp32.npz:", len(out), "arrays;",
+          "max |paged_kf1 - sdpa_kf1| =",
+          max(float(np.abs(out[f'paged_kf1_frame{i}'] - out[f'sdpa_kf1_frame{i}']).max()) for i in range(2, 10)))
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    _import_reference(args.reference)
+    manager_traces()
+    paged_attention_values()
+    prepare_qkv_values()
+    block_stream_values()
