@@ -1,0 +1,180 @@
+/*
+ * gct_b200.h - C ABI of the B200 (sm_100a) attention backend for the streaming
+ * Geometric Context Transformer: paged two-stream KV cache manager, fused
+ * q/k-norm + RoPE + bf16 page append, tcgen05 paged/dense attention, split-KV merge.
+ *
+ * Conventions
+ *   - Every function returns an int status: 0 = ok, otherwise one of GCT_ERR_*.
+ *     Nothing throws, nothing traps.  gct_last_error() returns a thread-local,
+ *     human-readable description of the last failure on the calling thread.
+ *   - Pointers named *_dev are device pointers on the current CUDA device; `stream` is a
+ *     cudaStream_t passed as void*.  The library never allocates or frees device memory:
+ *     page pools, workspace and outputs belong to the caller.
+ *   - Token-major "NHD" tensors: [tokens, heads, head_dim] with head_dim == 64.
+ *   - dtype codes: GCT_F32 = 0, GCT_BF16 = 1.
+ *
+ * The comments cite the interface of the reference implementation (paths relative to the
+ * Robbyant/lingbot-map repository) that each entry point stands in for.
+ */
+#ifndef GCT_B200_H
+#define GCT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GCT_OK 0
+#define GCT_ERR_INVALID 1        /* bad argument (shape, dtype, null pointer, unbound pools) */
+#define GCT_ERR_POOL_EXHAUSTED 2 /* no free patch/special page: flashinfer_cache.py:489-494,533-537 */
+#define GCT_ERR_UNDERFLOW 3      /* rollback with nothing to roll back: flashinfer_cache.py:276-293 */
+#define GCT_ERR_CUDA 4           /* a CUDA runtime/driver call failed */
+#define GCT_ERR_DEVICE_STATUS 5  /* a kernel reported a bounded-wait timeout or an index check */
+#define GCT_ERR_CAPACITY 6       /* caller-provided buffer or workspace too small */
+
+#define GCT_F32 0
+#define GCT_BF16 1
+
+#define GCT_ROPE_NONE 0
+#define GCT_ROPE_2D 1 /* rotate-half inside each 32-wide half: lingbot_map/layers/rope.py:134-198 */
+#define GCT_ROPE_3D 2 /* interleaved pairs (2m,2m+1): lingbot_map/layers/rope.py:435-461 */
+
+typedef struct gct_mgr gct_mgr_t;
+
+/* Geometry of one cache manager: arguments of FlashInferKVCacheManager.__init__
+ * (lingbot_map/layers/flashinfer_cache.py:75-90). */
+typedef struct gct_mgr_config {
+  int32_t num_blocks;
+  int32_t tokens_per_frame;   /* patches + specials, specials first */
+  int32_t num_heads;
+  int32_t head_dim;           /* must be 64 */
+  int32_t num_special_tokens; /* 6 */
+  int32_t scale_frames;       /* 8 */
+  int32_t sliding_window;     /* 64 */
+  int32_t max_total_frames;   /* sizes the special-page pool */
+} gct_mgr_config_t;
+
+/* Derived sizes (flashinfer_cache.py:100-138). */
+typedef struct gct_mgr_geometry {
+  int32_t page_size;       /* tokens per page = patches per frame */
+  int32_t max_patch_pages; /* scale + window + 16 */
+  int32_t max_num_pages;   /* patch pages + special pages */
+  int64_t pool_bytes;      /* bytes of one block's pool [max_num_pages,2,page_size,H,64] bf16 */
+} gct_mgr_geometry_t;
+
+const char* gct_last_error(void);
+int gct_version(void);
+
+/* ---- cache manager: host bookkeeping (bit-exact with the reference) ------------------- */
+
+/* FlashInferKVCacheManager.__init__ (flashinfer_cache.py:75-196), minus allocation. */
+int gct_mgr_create(gct_mgr_t** out, const gct_mgr_config_t* cfg, gct_mgr_geometry_t* geo_out);
+int gct_mgr_destroy(gct_mgr_t* m);
+
+/* Hand the manager the caller-allocated device memory: one bf16 pool per block laid out
+ * [max_num_pages, 2 (K,V), page_size, H, 64] (flashinfer_cache.py:141-148) and a workspace for
+ * split-KV partial results, the device page table and the status word (the reference's
+ * workspace_buffer, flashinfer_cache.py:184-186).  Needs a CUDA device. */
+int gct_mgr_bind(gct_mgr_t* m, void* const* pools_dev, void* workspace_dev, size_t workspace_bytes);
+/* Smallest workspace gct_mgr_bind accepts for this geometry. */
+int gct_mgr_workspace_bytes(const gct_mgr_t* m, size_t* bytes_out);
+
+/* append_frame (flashinfer_cache.py:202-227, 474-553): allocate one patch page (LIFO), route it to
+ * the scale or window list, append the specials to the special stream, and write K/V as bf16.
+ * k_dev/v_dev: [tokens_per_frame, H, 64] contiguous, dtype GCT_F32 or GCT_BF16. */
+int gct_mgr_append(gct_mgr_t* m, int block, const void* k_dev, int k_dtype, const void* v_dev, int v_dtype,
+                   void* stream);
+/* Same bookkeeping without touching device memory (tests, dry runs, replicas that do not own a page). */
+int gct_mgr_append_bookkeeping(gct_mgr_t* m, int block);
+
+/* Fused tail of FlashInferAttention.prepare_qkv (lingbot_map/layers/attention.py:413-426) and
+ * append_frame: from the qkv Linear output [tokens, 3*H*64] apply LayerNorm(64) to q and k
+ * (attention.py:58-59,415), rotate them with the per-token cos/sin table `rope_cs_dev`
+ * [tokens, 32, 2] fp32, write q as bf16 NHD to q_out_dev and K/V straight into their pages. */
+int gct_mgr_append_fused(gct_mgr_t* m, int block, const void* qkv_dev, int qkv_dtype, int64_t qkv_row_stride,
+                         const float* qn_w_dev, const float* qn_b_dev, const float* kn_w_dev, const float* kn_b_dev,
+                         const float* rope_cs_dev, int rope_mode, void* q_out_dev, void* stream);
+
+/* evict_frames (flashinfer_cache.py:229-254): no-op while eviction is deferred. */
+int gct_mgr_evict(gct_mgr_t* m, int block, int sliding_window);
+/* execute_deferred_eviction (flashinfer_cache.py:256-266). */
+int gct_mgr_exec_deferred(gct_mgr_t* m, int block, int sliding_window);
+/* the _defer_eviction attribute (flashinfer_cache.py:172-175; set by block.py:258-263). */
+int gct_mgr_set_defer(gct_mgr_t* m, int defer);
+int gct_mgr_get_defer(const gct_mgr_t* m, int* defer_out);
+/* rollback_last_frame (flashinfer_cache.py:268-301). */
+int gct_mgr_rollback(gct_mgr_t* m, int block);
+/* reset (flashinfer_cache.py:423-432). */
+int gct_mgr_reset(gct_mgr_t* m);
+
+/* build_visible_page_table + compute_last_page_len (flashinfer_cache.py:438-470):
+ * page ids in the order scale, window, special. */
+int gct_mgr_visible_table(const gct_mgr_t* m, int block, int32_t* pages_out, int capacity, int* n_out,
+                          int* last_page_len_out);
+/* get_cache_stats (flashinfer_cache.py:303-322): frame_count, scale_pages, live_pages, free_pages,
+ * special_tokens, special_pages. */
+int gct_mgr_stats(const gct_mgr_t* m, int block, int64_t out[6]);
+/* Free lists in stack order (bottom first): which = 0 patch, 1 special. */
+int gct_mgr_free_list(const gct_mgr_t* m, int block, int which, int32_t* out, int capacity, int* n_out);
+
+/* ---- cache manager: attention ------------------------------------------------------ */
+
+/* The plan() half of compute_attention (flashinfer_cache.py:385-414): snapshot block 0's visible
+ * table and upload it; valid for every block until the next plan.  page_begin/page_end select a
+ * sub-range of the visible list (0, -1 = all) for KV-sharded execution. */
+int gct_mgr_plan(gct_mgr_t* m, int page_begin, int page_end, void* stream);
+
+/* The run() half (flashinfer_cache.py:416-421): softmax(q k^T / 8) v over the planned pages of `block`.
+ * q_dev [n_q, H, 64] (GCT_F32 or GCT_BF16; cast to bf16 first as the reference does, :419),
+ * out_dev [n_q, H, 64] bf16.  lse_dev (optional, may be NULL) receives the natural log-sum-exp
+ * [n_q, H] fp32. */
+int gct_mgr_attention(gct_mgr_t* m, int block, const void* q_dev, int q_dtype, int n_q, void* out_dev,
+                      float* lse_dev, void* stream);
+/* Same, but leaves the result un-rounded: out_f32_dev [n_q, H, 64] fp32 plus lse_dev (required).
+ * Used when partial results over a page sub-range are merged across GPUs. */
+int gct_mgr_attention_partial(gct_mgr_t* m, int block, const void* q_dev, int q_dtype, int n_q,
+                              float* out_f32_dev, float* lse_dev, void* stream);
+
+/* Reads the device status word (blocks on `stream`): 0 if no kernel reported a problem. */
+int gct_mgr_device_status(gct_mgr_t* m, void* stream, int* status_out);
+/* Number of kernels this manager has launched since creation. */
+int gct_mgr_launch_count(const gct_mgr_t* m, int64_t* count_out);
+
+/* ---- stand-alone operators --------------------------------------------------------- */
+
+/* Dense non-causal attention, the F.scaled_dot_product_attention call of Attention.forward
+ * (lingbot_map/layers/attention.py:76) and of the phase-1 branch (attention.py:490).
+ * q [batch, n_q, H, 64], k/v [batch, n_kv, H, 64], all bf16, arbitrary element strides
+ * (multiples of 8 elements; head_dim contiguous); out [batch, n_q, H, 64] bf16 contiguous.
+ * workspace is needed only when the call splits the KV range (n_kv large, few query tiles). */
+int gct_attn_dense(const void* q_dev, const void* k_dev, const void* v_dev, void* out_dev, int batch, int n_q,
+                   int n_kv, int heads, const int64_t q_strides[3], const int64_t k_strides[3],
+                   const int64_t v_strides[3], void* workspace_dev, size_t workspace_bytes, void* stream);
+
+/* q/k LayerNorm + RoPE + bf16 cast for one batch of frames without a cache (frame blocks,
+ * attention.py:67-73): qkv [tokens, 3*H*64] -> q,k,v bf16 [tokens, H, 64].  rope_cs_dev is indexed
+ * by (token % tokens_per_frame). */
+int gct_prep_qkv(const void* qkv_dev, int qkv_dtype, int64_t qkv_row_stride, int tokens, int tokens_per_frame,
+                 int heads, const float* qn_w_dev, const float* qn_b_dev, const float* kn_w_dev,
+                 const float* kn_b_dev, const float* rope_cs_dev, int rope_mode, void* q_out_dev, void* k_out_dev,
+                 void* v_out_dev, void* stream);
+
+/* cos/sin tables [tokens_per_frame, 32, 2] fp32.
+ * 3-D (rope.py:293-433): time index f, specials at (f,i,i), patch (r,c) at (f,ns+r,ns+c), theta 1e4,
+ * axis split 20/22/22, angles in fp64.  2-D (rope.py:88-122, base.py:416-442): specials at (0,0),
+ * patches at (r+1,c+1), base 100, angles in fp32. */
+int gct_rope3d_table(int frame_index, int pph, int ppw, int num_special, float* cs_out_dev, void* stream);
+int gct_rope2d_table(int pph, int ppw, int num_special, float base, float* cs_out_dev, void* stream);
+
+/* Merge G partial attention results: out = sum_g e^{lse_g-m} O_g / sum_g e^{lse_g-m}.
+ * parts_dev [G, n_q, H, 64] fp32 (each already normalised), lse_dev [G, n_q, H] fp32,
+ * out_dev [n_q, H, 64] bf16; lse_out_dev optional. */
+int gct_lse_merge(const float* parts_dev, const float* lse_dev, int groups, int n_q, int heads, void* out_dev,
+                  float* lse_out_dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GCT_B200_H */

@@ -1,0 +1,544 @@
+// Paged / dense non-causal attention for sm_100a: softmax(Q K^T / 8) V with head_dim 64, bf16 operands,
+// fp32 accumulation.  Stands in for the reference's FlashInfer BatchPrefillWithPagedKVCacheWrapper.run
+// (lingbot_map/layers/flashinfer_cache.py:416-421) and its F.scaled_dot_product_attention calls
+// (lingbot_map/layers/attention.py:76,490).
+//
+// One CTA owns QT (1 or 2) query tiles of 128 rows of one head and one contiguous range of KV blocks
+// (128 tokens each).  Warp roles:
+//   warps [0, 4*QT)   softmax: one thread per query row; warp w reads TMEM lanes 32*(w%4)..+31
+//   warp  4*QT        producer: TMA loads of Q once and of K/V blocks into a 3-stage ring
+//   warp  4*QT+1      MMA issuer: tcgen05.mma  S = Q K^T (128x128x64)  and  PV = P V (128x64x128)
+// TMEM columns: S tile t at [128 t, 128 t + 128), PV tile t at [128 QT + 64 t, +64).
+// Per KV block j and tile t:
+//   MMA:      S_j -> commit s_full[t]
+//   softmax:  wait s_full; row max; (wait pv_full of block j-1; O = O*alpha + PV_{j-1});
+//             P = exp2(S*c - m*c) as bf16 into swizzled smem; arrive p_full[t]
+//   MMA:      wait p_full; issue S_{j+1}; issue PV_j = P V_j -> commit pv_full[t];
+//             after the last tile commit kv_empty[stage]
+// The running output stays in registers (64 fp32 per row); every mbarrier wait is bounded and
+// reports through the status word instead of spinning forever.
+#include "gct_common.h"
+
+namespace gct {
+namespace {
+
+constexpr int kStages = 3;
+constexpr uint32_t kTileBytes = 128 * 64 * 2;      // one 128x64 bf16 tile, 128B-swizzled
+constexpr uint32_t kPBytes = 2 * kTileBytes;       // P tile 128x128 bf16 = two K-halves
+constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at 2 GHz; only reached on a bug
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---- mbarrier ---------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting (this or another thread ran out of time, or
+// another CTA flagged the status word); the caller then leaves its role loop.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* cta_abort, int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 0u) {
+      if (*cta_abort) return false;
+      if ((it & 1023u) == 0u && *reinterpret_cast<volatile int*>(status) != 0) {
+        *cta_abort = 1;
+        return false;
+      }
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *cta_abort = 1;
+        atomicCAS(status, 0, kStatusWaitTimeout);
+        return false;
+      }
+    }
+  }
+}
+
+// ---- TMA ---------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tm) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");
+}
+
+// ---- tcgen05 ------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], bf16 x bf16 -> fp32, issued by one thread.
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128B swizzle, descriptor version 1 (sm_100).
+//   bits [0,14)  start address >> 4      bits [16,30) leading byte offset >> 4
+//   bits [32,46) stride byte offset >> 4 bits [46,48) version = 1      bits [61,64) layout = 2 (SWIZZLE_128B)
+// K-major tile (rows of 128 B, 8-row groups 1024 B apart): SBO = 1024, LBO unused (1).
+// MN-major tile (k-rows of 128 B holding 64 contiguous MN elements): SBO = 1024 between 8-k-row groups.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return static_cast<uint64_t>((addr >> 4) & 0x3FFFu) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
+         (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor (kind::f16): c_format F32 (bit 4), a/b format BF16 (bits 7, 10),
+// b_major at bit 16 (1 = MN-major), N>>3 at bits [17,23), M>>4 at bits [24,29).
+constexpr uint32_t kIdescS = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+constexpr uint32_t kIdescPV =
+    (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+struct KernelArgs {
+  const int32_t* page_table;
+  int n_pages, page_len, last_page_len, blocks_per_page, total_blocks;
+  int n_q, heads, batch, q_groups, splits, final_bf16;
+  float scale_log2;
+  __nv_bfloat16* out;
+  float* part_o;
+  float* part_lse;
+  int* status;
+};
+
+template <int QT>
+struct SmemLayout {
+  static constexpr uint32_t q_off = 0;
+  static constexpr uint32_t k_off = q_off + QT * kTileBytes;
+  static constexpr uint32_t v_off = k_off + kStages * kTileBytes;
+  static constexpr uint32_t p_off = v_off + kStages * kTileBytes;
+  static constexpr uint32_t bar_off = p_off + QT * kPBytes;
+  // barriers: q_full, k_full[ST], v_full[ST], kv_empty[ST], s_full[QT], p_full[QT], pv_full[QT]
+  static constexpr int n_bars = 1 + 3 * kStages + 3 * QT;
+  static constexpr uint32_t misc_off = bar_off + n_bars * 8;
+  static constexpr uint32_t total = misc_off + 16;
+};
+
+template <int QT>
+__global__ void __launch_bounds__(QT * 128 + 64, 1)
+gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const KernelArgs a) {
+  using L = SmemLayout<QT>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bars = sbase + L::bar_off;
+  auto bar_q_full = [&]() { return bars; };
+  auto bar_k_full = [&](int s) { return bars + 8u * (1 + s); };
+  auto bar_v_full = [&](int s) { return bars + 8u * (1 + kStages + s); };
+  auto bar_kv_empty = [&](int s) { return bars + 8u * (1 + 2 * kStages + s); };
+  auto bar_s_full = [&](int t) { return bars + 8u * (1 + 3 * kStages + t); };
+  auto bar_p_full = [&](int t) { return bars + 8u * (1 + 3 * kStages + QT + t); };
+  auto bar_pv_full = [&](int t) { return bars + 8u * (1 + 3 * kStages + 2 * QT + t); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::misc_off);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(smem + L::misc_off + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr int kProducerWarp = 4 * QT;
+  constexpr int kMmaWarp = 4 * QT + 1;
+  constexpr uint32_t kTmemCols = (QT == 2) ? 512u : 256u;
+
+  // ---- work coordinates ----
+  int idx = blockIdx.x;
+  const int qg = idx % a.q_groups;
+  idx /= a.q_groups;
+  const int split = idx % a.splits;
+  idx /= a.splits;
+  const int h = idx % a.heads;
+  const int b = idx / a.heads;
+  const int g0 = static_cast<int>(static_cast<long long>(split) * a.total_blocks / a.splits);
+  const int g1 = static_cast<int>(static_cast<long long>(split + 1) * a.total_blocks / a.splits);
+  const int nblk = g1 - g0;
+
+  // ---- set-up ----
+  if (threadIdx.x == 0) {
+    mbar_init(bar_q_full(), 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_k_full(s), 1);
+      mbar_init(bar_v_full(s), 1);
+      mbar_init(bar_kv_empty(s), 1);
+    }
+    for (int t = 0; t < QT; ++t) {
+      mbar_init(bar_s_full(t), 1);
+      mbar_init(bar_p_full(t), 128);
+      mbar_init(bar_pv_full(t), 1);
+    }
+    *cta_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+  }
+  if (warp == kProducerWarp && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == kProducerWarp) {
+    // =========================== producer ===========================
+    if (lane == 0) {
+      mbar_arrive_expect_tx(bar_q_full(), QT * kTileBytes);
+      for (int t = 0; t < QT; ++t)
+        tma_load_4d(sbase + L::q_off + t * kTileBytes, &tm_q, bar_q_full(), 0, h, (qg * QT + t) * kTileM, b);
+      int page = b, cur_pi = -1;
+      for (int j = 0; j < nblk; ++j) {
+        const int st = j % kStages;
+        const uint32_t ph = (j / kStages) & 1;
+        if (!mbar_wait(bar_kv_empty(st), ph ^ 1u, cta_abort, a.status)) break;
+        const int g = g0 + j;
+        const int pi = g / a.blocks_per_page;
+        const int jb = g - pi * a.blocks_per_page;
+        if (a.page_table != nullptr && pi != cur_pi) {
+          page = __ldg(a.page_table + pi);
+          cur_pi = pi;
+        }
+        mbar_arrive_expect_tx(bar_k_full(st), kTileBytes);
+        tma_load_4d(sbase + L::k_off + st * kTileBytes, &tm_k, bar_k_full(st), 0, h, jb * kBlockN, page);
+        mbar_arrive_expect_tx(bar_v_full(st), kTileBytes);
+        tma_load_4d(sbase + L::v_off + st * kTileBytes, &tm_v, bar_v_full(st), 0, h, jb * kBlockN, page);
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      auto issue_s = [&](int t, int st) {
+        const uint64_t ad = smem_desc(sbase + L::q_off + t * kTileBytes, 16, 1024);
+        const uint64_t bd = smem_desc(sbase + L::k_off + st * kTileBytes, 16, 1024);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)   // 64 = 4 x K16; +32 B per step inside the 128 B swizzle row
+          umma_ss(tmem_base + t * 128, ad + 2 * k, bd + 2 * k, kIdescS, k > 0);
+      };
+      auto issue_pv = [&](int t, int st) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {   // 128 tokens = 8 x K16
+          const uint64_t ad =
+              smem_desc(sbase + L::p_off + t * kPBytes + (k >> 2) * kTileBytes + (k & 3) * 32, 16, 1024);
+          const uint64_t bd = smem_desc(sbase + L::v_off + st * kTileBytes + k * 2048, 16, 1024);
+          umma_ss(tmem_base + QT * 128 + t * 64, ad, bd, kIdescPV, k > 0);
+        }
+      };
+      bool ok = mbar_wait(bar_q_full(), 0, cta_abort, a.status) && mbar_wait(bar_k_full(0), 0, cta_abort, a.status);
+      if (ok) {
+        tc_fence_after();
+        for (int t = 0; t < QT; ++t) {
+          issue_s(t, 0);
+          tc_commit(bar_s_full(t));
+        }
+      }
+      for (int j = 0; ok && j < nblk; ++j) {
+        const int st = j % kStages;
+        const uint32_t ph = (j / kStages) & 1;
+        for (int t = 0; t < QT; ++t) {
+          if (!(ok = mbar_wait(bar_p_full(t), j & 1, cta_abort, a.status))) break;
+          tc_fence_after();
+          if (j + 1 < nblk) {
+            const int st1 = (j + 1) % kStages;
+            if (t == 0 && !(ok = mbar_wait(bar_k_full(st1), ((j + 1) / kStages) & 1, cta_abort, a.status))) break;
+            tc_fence_after();
+            issue_s(t, st1);
+            tc_commit(bar_s_full(t));
+          }
+          if (t == 0 && !(ok = mbar_wait(bar_v_full(st), ph, cta_abort, a.status))) break;
+          tc_fence_after();
+          issue_pv(t, st);
+          tc_commit(bar_pv_full(t));
+        }
+        if (ok) tc_commit(bar_kv_empty(st));
+      }
+    }
+  } else {
+    // =========================== softmax ===========================
+    const int t = warp >> 2;                       // query tile of this warp
+    const int row = ((warp & 3) << 5) | lane;      // row inside the tile == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) << 5) << 16;
+    const uint32_t s_addr = tmem_base + lane_addr + t * 128;
+    const uint32_t pv_addr = tmem_base + lane_addr + QT * 128 + t * 64;
+    uint8_t* p_row = smem + L::p_off + t * kPBytes + row * 128;
+    const uint32_t sw = static_cast<uint32_t>(row & 7);
+    const float c = a.scale_log2;
+    float o[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) o[i] = 0.f;
+    float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
+    bool ok = true;
+    uint32_t r[32];
+
+    for (int j = 0; j < nblk; ++j) {
+      if (!(ok = mbar_wait(bar_s_full(t), j & 1, cta_abort, a.status))) break;
+      tc_fence_after();
+      // valid tokens of this block
+      const int g = g0 + j;
+      const int pi = g / a.blocks_per_page;
+      const int jb = g - pi * a.blocks_per_page;
+      const int plen = (pi == a.n_pages - 1) ? a.last_page_len : a.page_len;
+      const int valid = min(kBlockN, plen - jb * kBlockN);
+
+      // pass 1: row maximum
+      float mx = m;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        tmem_ld32(s_addr + cc * 32, r);
+        tmem_wait_ld();
+        if (valid >= kBlockN) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (cc * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      }
+      const float alpha = fast_exp2((m - mx) * c);   // m = -inf on the first block: exp2(-inf) = 0
+      // fold in the PV product of the previous block (it was computed against the previous maximum)
+      if (j > 0) {
+        if (!(ok = mbar_wait(bar_pv_full(t), (j - 1) & 1, cta_abort, a.status))) break;
+        tc_fence_after();
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          tmem_ld32(pv_addr + hh * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[hh * 32 + i] = fmaf(o[hh * 32 + i], alpha_prev, __uint_as_float(r[i]));
+        }
+      }
+      // pass 2: P = exp2(S*c - m*c), row sum, bf16 into the swizzled P tile
+      const float mc = mx * c;
+      float rs = 0.f;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        tmem_ld32(s_addr + cc * 32, r);
+        tmem_wait_ld();
+        float e[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = fast_exp2(fmaf(__uint_as_float(r[i]), c, -mc));
+          if (valid < kBlockN && cc * 32 + i >= valid) x = 0.f;
+          e[i] = x;
+          rs += x;
+        }
+        // columns [32cc, 32cc+32): K-half (cc>>1), 16-byte chunks 4*(cc&1)..+3, XOR-swizzled with (row & 7)
+        uint8_t* half = p_row + (cc >> 1) * kTileBytes;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 w;
+          w.x = pack_bf16x2(e[q4 * 8 + 0], e[q4 * 8 + 1]);
+          w.y = pack_bf16x2(e[q4 * 8 + 2], e[q4 * 8 + 3]);
+          w.z = pack_bf16x2(e[q4 * 8 + 4], e[q4 * 8 + 5]);
+          w.w = pack_bf16x2(e[q4 * 8 + 6], e[q4 * 8 + 7]);
+          const uint32_t chunk = static_cast<uint32_t>((cc & 1) * 4 + q4) ^ sw;
+          *reinterpret_cast<uint4*>(half + chunk * 16) = w;
+        }
+      }
+      l = fmaf(l, alpha, rs);
+      m = mx;
+      alpha_prev = alpha;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P visible to the tensor core
+      tc_fence_before();
+      mbar_arrive(bar_p_full(t));
+    }
+    if (ok && nblk > 0) {
+      ok = mbar_wait(bar_pv_full(t), (nblk - 1) & 1, cta_abort, a.status);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          tmem_ld32(pv_addr + hh * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[hh * 32 + i] = fmaf(o[hh * 32 + i], alpha_prev, __uint_as_float(r[i]));
+        }
+      }
+    }
+    const int qrow = (qg * QT + t) * kTileM + row;
+    if (ok && nblk > 0 && qrow < a.n_q) {
+      const float inv = 1.f / l;
+      const size_t rowidx = (static_cast<size_t>(b) * a.n_q + qrow) * a.heads + h;
+      if (a.final_bf16) {
+        uint4* dst = reinterpret_cast<uint4*>(a.out + rowidx * kHeadDim);
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) {
+          uint4 w;
+          w.x = pack_bf16x2(o[q4 * 8 + 0] * inv, o[q4 * 8 + 1] * inv);
+          w.y = pack_bf16x2(o[q4 * 8 + 2] * inv, o[q4 * 8 + 3] * inv);
+          w.z = pack_bf16x2(o[q4 * 8 + 4] * inv, o[q4 * 8 + 5] * inv);
+          w.w = pack_bf16x2(o[q4 * 8 + 6] * inv, o[q4 * 8 + 7] * inv);
+          dst[q4] = w;
+        }
+      } else {
+        const size_t prow = static_cast<size_t>(split) * a.batch * a.n_q * a.heads + rowidx;
+        float4* dst = reinterpret_cast<float4*>(a.part_o + prow * kHeadDim);
+#pragma unroll
+        for (int q4 = 0; q4 < 16; ++q4)
+          dst[q4] = make_float4(o[q4 * 4 + 0] * inv, o[q4 * 4 + 1] * inv, o[q4 * 4 + 2] * inv, o[q4 * 4 + 3] * inv);
+        a.part_lse[prow] = (m * c + log2f(l)) * 0.6931471805599453f;
+      }
+    }
+  }
+
+  // ---- teardown: every thread arrives here, also after an abort ----
+  if (*cta_abort) {
+    // give copies and MMAs that may still be in flight time to land before TMEM and smem are released
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+
+int attention_smem_bytes(int qt) {
+  return static_cast<int>((qt == 2 ? SmemLayout<2>::total : SmemLayout<1>::total) + 1024);
+}
+
+int launch_attention(const AttnLaunch& a, cudaStream_t stream) {
+  if (a.n_q <= 0 || a.heads <= 0 || a.batch <= 0 || a.n_pages <= 0 || a.page_len <= 0 || a.last_page_len <= 0 ||
+      a.last_page_len > a.page_len)
+    return fail(GCT_ERR_INVALID, "attention: bad shape");
+  if (a.q_tiles_per_cta != 1 && a.q_tiles_per_cta != 2) return fail(GCT_ERR_INVALID, "attention: q_tiles_per_cta");
+  if (a.status == nullptr) return fail(GCT_ERR_INVALID, "attention: status word missing");
+  KernelArgs k;
+  k.page_table = a.page_table;
+  k.n_pages = a.n_pages;
+  k.page_len = a.page_len;
+  k.last_page_len = a.last_page_len;
+  k.blocks_per_page = (a.page_len + kBlockN - 1) / kBlockN;
+  k.total_blocks = (a.n_pages - 1) * k.blocks_per_page + (a.last_page_len + kBlockN - 1) / kBlockN;
+  k.n_q = a.n_q;
+  k.heads = a.heads;
+  k.batch = a.batch;
+  const int rows_per_cta = kTileM * a.q_tiles_per_cta;
+  k.q_groups = (a.n_q + rows_per_cta - 1) / rows_per_cta;
+  k.splits = a.splits;
+  k.final_bf16 = a.final_bf16 ? 1 : 0;
+  k.scale_log2 = 0.125f * 1.4426950408889634f;   // 1/sqrt(64) * log2(e)
+  k.out = a.out;
+  k.part_o = a.part_o;
+  k.part_lse = a.part_lse;
+  k.status = a.status;
+  if (a.splits < 1 || a.splits > k.total_blocks) return fail(GCT_ERR_INVALID, "attention: splits out of range");
+  if (a.final_bf16 && (a.splits != 1 || a.out == nullptr)) return fail(GCT_ERR_INVALID, "attention: final output needs splits == 1");
+  if (!a.final_bf16 && (a.part_o == nullptr || a.part_lse == nullptr))
+    return fail(GCT_ERR_INVALID, "attention: partial buffers missing");
+  const long long grid = static_cast<long long>(k.q_groups) * a.splits * a.heads * a.batch;
+  if (grid <= 0 || grid > 0x7fffffffLL) return fail(GCT_ERR_INVALID, "attention: grid too large");
+  const int smem = attention_smem_bytes(a.q_tiles_per_cta);
+  if (a.q_tiles_per_cta == 2) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      GCT_CUDA_CHECK(cudaFuncSetAttribute(gct_attn_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      attr_set = true;
+    }
+    gct_attn_kernel<2><<<static_cast<unsigned>(grid), 2 * 128 + 64, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
+  } else {
+    static bool attr_set = false;
+    if (!attr_set) {
+      GCT_CUDA_CHECK(cudaFuncSetAttribute(gct_attn_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      attr_set = true;
+    }
+    gct_attn_kernel<1><<<static_cast<unsigned>(grid), 128 + 64, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
+  }
+  GCT_CUDA_CHECK(cudaGetLastError());
+  return GCT_OK;
+}
+
+void choose_attention_config(int n_q_tiles, int heads_x_batch, int total_blocks, int num_sms, int max_splits,
+                             int* q_tiles_per_cta, int* splits) {
+  // Cost model in units of "one KV block for one CTA": a CTA with two query tiles takes about as long
+  // per block as one with a single tile takes for 0.6 blocks-worth of its pair; every CTA pays a fixed
+  // prologue/epilogue of about two blocks.  Pick the cheapest (tiles per CTA, splits).
+  double best = 1e300;
+  int best_qt = 1, best_s = 1;
+  for (int qt = 2; qt >= 1; --qt) {
+    const long long items = static_cast<long long>((n_q_tiles + qt - 1) / qt) * heads_x_batch;
+    const double per_block = (qt == 2) ? 1.0 : 0.6;
+    const int smax = total_blocks < max_splits ? total_blocks : max_splits;
+    for (int s = 1; s <= smax; ++s) {
+      const long long ctas = items * s;
+      const long long waves = (ctas + num_sms - 1) / num_sms;
+      const int blocks = (total_blocks + s - 1) / s;
+      const double cost = static_cast<double>(waves) * (blocks * per_block + 2.0) + (s > 1 ? 0.5 : 0.0);
+      if (cost < best - 1e-9) {
+        best = cost;
+        best_qt = qt;
+        best_s = s;
+      }
+    }
+  }
+  *q_tiles_per_cta = best_qt;
+  *splits = best_s;
+}
+
+}  // namespace gct

@@ -1,0 +1,98 @@
+// Shared declarations of the GCT B200 backend: error plumbing and the launch interfaces
+// between the C-ABI layer (gct_manager.cu) and the kernels.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/gct_b200.h"
+
+namespace gct {
+
+// Thread-local error text behind gct_last_error().
+void set_error(const std::string& msg);
+int fail(int code, const std::string& msg);
+
+#define GCT_CUDA_CHECK(expr)                                                                  \
+  do {                                                                                        \
+    cudaError_t _e = (expr);                                                                  \
+    if (_e != cudaSuccess)                                                                    \
+      return ::gct::fail(GCT_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e));   \
+  } while (0)
+
+constexpr int kHeadDim = 64;
+constexpr int kBlockN = 128;   // KV tokens per attention block (one UMMA N tile)
+constexpr int kTileM = 128;    // query rows per UMMA tile
+
+// Codes written to the device status word by kernels (0 = ok).
+constexpr int kStatusWaitTimeout = 1;   // a bounded mbarrier wait gave up
+constexpr int kStatusBadIndex = 2;      // a page id / token offset failed its bounds check
+
+// ---- attention -------------------------------------------------------------------------
+// KV is a list of pages; every page but the last holds page_len tokens, the last one
+// last_page_len.  A page is cut into blocks of kBlockN tokens (the tail block of a page is
+// partial and masked).  With page_table == nullptr page i of batch item b is page id b
+// (dense K/V: one page per batch item).
+struct AttnLaunch {
+  CUtensorMap tm_q, tm_k, tm_v;      // 4-D maps (d, head, token, page|batch), box {64,1,128,1}, 128B swizzle
+  const int32_t* page_table = nullptr;
+  int n_pages = 0;
+  int page_len = 0;
+  int last_page_len = 0;
+  int n_q = 0, heads = 0, batch = 1;
+  int q_tiles_per_cta = 2;           // 1 or 2
+  int splits = 1;
+  bool final_bf16 = true;            // true: write bf16 out (requires splits == 1); false: partials
+  __nv_bfloat16* out = nullptr;      // [batch, n_q, H, 64]
+  float* part_o = nullptr;           // [splits, batch, n_q, H, 64] normalised partial outputs
+  float* part_lse = nullptr;         // [splits, batch, n_q, H] natural log-sum-exp
+  int* status = nullptr;             // device status word
+};
+int launch_attention(const AttnLaunch& a, cudaStream_t stream);
+int attention_smem_bytes(int q_tiles_per_cta);
+
+// Encode a 4-D bf16 tensor map {64, heads, tokens, pages} with the given element strides
+// (head, token, page) and the box {64,1,128,1}.
+int make_tensor_map(CUtensorMap* out, const void* base, int heads, int64_t tokens, int64_t pages,
+                    int64_t head_stride, int64_t token_stride, int64_t page_stride);
+
+// Pick (q_tiles_per_cta, splits) for a problem: n_q_tiles query tiles of 128 rows per (head,batch),
+// total_blocks KV blocks, on num_sms SMs, with at most max_splits partial results.
+void choose_attention_config(int n_q_tiles, int heads_x_batch, int total_blocks, int num_sms, int max_splits,
+                             int* q_tiles_per_cta, int* splits);
+
+// ---- elementwise kernels ---------------------------------------------------------------
+struct PrepLaunch {
+  // sources: rows of 64 elements; element strides between tokens and heads
+  const void* q_src = nullptr; const void* k_src = nullptr; const void* v_src = nullptr;
+  int src_dtype_qk = GCT_BF16;       // dtype of q_src and k_src
+  int src_dtype_v = GCT_BF16;
+  int64_t src_token_stride = 0, src_head_stride = 64;
+  int tokens = 0, heads = 0, tokens_per_frame = 0;
+  const float* qn_w = nullptr; const float* qn_b = nullptr;   // null: no LayerNorm
+  const float* kn_w = nullptr; const float* kn_b = nullptr;
+  const float* rope_cs = nullptr;    // [tokens_per_frame, 32, 2] cos,sin; null or mode NONE: no rotation
+  int rope_mode = GCT_ROPE_NONE;
+  __nv_bfloat16* q_out = nullptr;    // [tokens, H, 64] or null
+  // K/V destination, dense: [tokens, H, 64]
+  __nv_bfloat16* k_out = nullptr; __nv_bfloat16* v_out = nullptr;
+  // K/V destination, paged (k_out == null): pool [pages, 2, page_size, H, 64]
+  __nv_bfloat16* pool = nullptr;
+  int page_size = 0, num_pages = 0, num_special = 0;
+  int patch_page = -1;               // tokens >= num_special go to row (token - num_special) of this page
+  int sp_page0 = -1, sp_off0 = 0, sp_n0 = 0, sp_page1 = -1;   // specials: first sp_n0 at sp_off0 of page0, rest at row 0.. of page1
+  int* status = nullptr;
+};
+int launch_prep(const PrepLaunch& p, cudaStream_t stream);
+
+int launch_cast_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream_t stream);
+int launch_merge(const float* parts, const float* lse, int groups, int64_t rows /* n_q*H */, __nv_bfloat16* out_bf16,
+                 float* out_f32, float* lse_out, cudaStream_t stream);
+int launch_rope3d_table(int f, int pph, int ppw, int ns, float* cs, cudaStream_t stream);
+int launch_rope2d_table(int pph, int ppw, int ns, float base, float* cs, cudaStream_t stream);
+
+}  // namespace gct

@@ -1,0 +1,277 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle and the reference's golden outputs.
+
+Tolerances (bf16 operands, fp32 accumulation): max-abs 2e-2 and cosine >= 0.9999 in float64 against the
+float64 oracle evaluated on the same bf16-rounded inputs."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import seeded
+import lingbot_map_b200 as P
+from lingbot_map_b200 import _lib
+from oracle import gct_oracle as O
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(__file__), "golden")
+DEV = "cuda:0"
+
+
+def cosine64(a, b):
+    a = np.asarray(a, np.float64).ravel()
+    b = np.asarray(b, np.float64).ravel()
+    return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-300))
+
+
+def assert_close(got, want, tag, max_abs=2e-2, cos=0.9999):
+    got = got.float().cpu().numpy() if torch.is_tensor(got) else got
+    d = float(np.abs(got.astype(np.float64) - want).max())
+    c = cosine64(got, want)
+    assert np.isfinite(got).all(), tag
+    assert d <= max_abs and c >= cos, f"{tag}: max_abs={d:.3e} cosine={c:.7f}"
+
+
+def bf(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(DEV).to(torch.bfloat16)
+
+
+def r(x):
+    return O.bf16_round(x).astype(np.float64)
+
+
+# ---------------------------------------------------------------- paged attention vs reference goldens
+@pytest.mark.parametrize("name", ["p20", "p150", "p300"])
+@pytest.mark.parametrize("kdtype", ["bf16", "f32"])
+def test_paged_attention_golden(name, kdtype):
+    z = np.load(os.path.join(G, "paged_attention_fp32.npz"))
+    g = json.loads(bytes(z["meta_json"]).decode())[name]
+    tpf, H, vs = g["tokens_per_frame"], g["heads"], g["value_scale"]
+    m = P.B200KVCacheManager(1, g["scale"] + g["window"] + 16, tpf, H, 64, device=DEV, scale_frames=g["scale"],
+                             sliding_window=g["window"], max_total_frames=g["max_total"])
+    orc = O.PagedCacheOracle(1, tpf, H, 64, scale_frames=g["scale"], sliding_window=g["window"],
+                             max_total_frames=g["max_total"])
+    for t in range(g["frames"] + 1):
+        k = seeded.randn(1000 + t, tpf, H, 64, scale=vs)
+        v = seeded.randn(2000 + t, tpf, H, 64, scale=vs)
+        q = seeded.randn(3000 + t, tpf, H, 64, scale=vs)
+        nonkf = t == g["frames"]
+        if nonkf:
+            m._defer_eviction = True
+            orc._defer_eviction = True
+        if kdtype == "bf16":
+            m.append_frame(0, bf(k), bf(v))
+            qd = bf(q)
+        else:   # fp32 K and q, bf16 V: what arrives under autocast
+            m.append_frame(0, torch.from_numpy(k).to(DEV), bf(v))
+            qd = torch.from_numpy(q).to(DEV)
+        m.evict_frames(0, g["scale"], g["window"])
+        orc.append_frame(0, r(k), r(v))
+        orc.evict_frames(0, g["scale"], g["window"])
+        assert m.build_visible_page_table(0) == orc.build_visible_page_table(0)
+        assert m.compute_last_page_len(0) == orc.compute_last_page_len(0)
+        out = m.compute_attention(0, qd)
+        assert out.dtype == torch.bfloat16 and tuple(out.shape) == (tpf, H, 64)
+        want = orc.compute_attention(0, r(q))
+        assert_close(out, want, f"{name} frame {t} vs oracle", max_abs=2e-2 * max(vs, 0.05))
+        key = f"{name}_out_nonkf" if nonkf else f"{name}_out_{t}"
+        if key in z:   # the reference's own fp32 result on the unrounded inputs
+            assert_close(out, z[key].astype(np.float64), f"{name} frame {t} vs reference", cos=0.9995)
+        if nonkf:
+            m.rollback_last_frame(0)
+            orc.rollback_last_frame(0)
+            m._defer_eviction = False
+    assert m.build_visible_page_table(0) == list(z[f"{name}_visible_end"])
+    # page contents are bit-exact bf16 roundings of what was appended
+    kk, vv = m._gather_kv(0)
+    ok, ov = orc.gather_kv(0)
+    assert (kk.float().cpu().numpy() == ok.astype(np.float32)).all()
+    assert (vv.float().cpu().numpy() == ov.astype(np.float32)).all()
+    assert m.device_status() == 0
+
+
+def test_empty_cache_returns_zeros():
+    m = P.B200KVCacheManager(1, 21, 26, 2, 64, device=DEV, scale_frames=2, sliding_window=3, max_total_frames=40)
+    q = torch.randn(26, 2, 64, device=DEV)
+    out = m.compute_attention(0, q)
+    assert out.shape == q.shape and float(out.abs().max()) == 0.0       # flashinfer_cache.py:368-370
+
+
+def test_plan_is_reused_across_blocks_and_lse():
+    """plan at block 0, run on every block (flashinfer_cache.py:385-421); lse output; partial + merge."""
+    tpf, H = 140, 3
+    m = P.B200KVCacheManager(3, 21, tpf, H, 64, device=DEV, scale_frames=1, sliding_window=2, max_total_frames=60)
+    orcs = O.PagedCacheOracle(3, tpf, H, 64, scale_frames=1, sliding_window=2, max_total_frames=60)
+    for t in range(7):
+        for b in range(3):
+            k, v = seeded.randn(10 * t + b, tpf, H, 64), seeded.randn(500 + 10 * t + b, tpf, H, 64)
+            m.append_frame(b, bf(k), bf(v))
+            m.evict_frames(b, 1, 2)
+            orcs.append_frame(b, r(k), r(v))
+            orcs.evict_frames(b, 1, 2)
+    for b in range(3):
+        q = seeded.randn(900 + b, tpf, H, 64)
+        out, lse = m.compute_attention(b, bf(q), return_lse=True)
+        kk, vv = orcs.gather_kv(b)
+        want, wl = O.attention(r(q), kk, vv)
+        assert_close(out, want, f"block {b}")
+        assert np.abs(lse.cpu().numpy() - wl).max() < 2e-3
+    # KV-sharded: two page sub-ranges, partial results merged by log-sum-exp
+    q = seeded.randn(77, tpf, H, 64)
+    n = len(m.build_visible_page_table(0))
+    parts, lses = [], []
+    for lo, hi in ((0, 2), (2, n)):
+        m.plan(lo, hi)
+        o, l = m.compute_attention_partial(1, bf(q))
+        parts.append(o)
+        lses.append(l)
+    merged = P.ops.lse_merge(torch.stack(parts), torch.stack(lses))
+    kk, vv = orcs.gather_kv(1)
+    assert_close(merged, O.attention(r(q), kk, vv)[0], "sharded merge")
+    assert m.device_status() == 0
+
+
+# ---------------------------------------------------------------- dense attention
+@pytest.mark.parametrize("B,Nq,Nkv,H", [(1, 1, 1, 1), (1, 6, 130, 2), (2, 130, 257, 3), (1, 1005, 1005, 2),
+                                         (3, 37, 128, 1), (1, 300, 2600, 2)])
+def test_dense_attention_vs_oracle(B, Nq, Nkv, H):
+    q, k, v = seeded.randn(1, B, Nq, H, 64), seeded.randn(2, B, Nkv, H, 64), seeded.randn(3, B, Nkv, H, 64)
+    out = P.ops.dense_attention(bf(q), bf(k), bf(v))
+    for b in range(B):
+        assert_close(out[b], O.attention(r(q[b]), r(k[b]), r(v[b]))[0], f"dense b={b}")
+    assert P.ops.device_status(DEV) == 0
+
+
+def test_dense_attention_strided_views():
+    """q/k/v as views into one qkv buffer [B, N, 3, H, 64] (the layout the qkv Linear produces)."""
+    B, N, H = 2, 200, 4
+    qkv = seeded.randn(9, B, N, 3, H, 64)
+    t = bf(qkv)
+    out = P.ops.dense_attention(t[:, :, 0], t[:, :, 1], t[:, :, 2])
+    for b in range(B):
+        assert_close(out[b], O.attention(r(qkv[b, :, 0]), r(qkv[b, :, 1]), r(qkv[b, :, 2]))[0], f"strided b={b}")
+
+
+def test_dense_attention_peaked_softmax():
+    """Large logits (|s| up to ~60): running-max rescaling must hold."""
+    Nq, Nkv, H = 140, 700, 2
+    q, k, v = seeded.randn(4, 1, Nq, H, 64, scale=3.0), seeded.randn(5, 1, Nkv, H, 64, scale=3.0), seeded.randn(6, 1, Nkv, H, 64)
+    out = P.ops.dense_attention(bf(q), bf(k), bf(v))
+    assert_close(out[0], O.attention(r(q[0]), r(k[0]), r(v[0]))[0], "peaked", max_abs=4e-2, cos=0.9995)
+
+
+# ---------------------------------------------------------------- fused prologue / append
+def _norm_params(seed):
+    names = ("q_norm.weight", "q_norm.bias", "k_norm.weight", "k_norm.bias")
+    w = [seeded.param_value(seed, n, (64,)) for n in names]
+    return w, [torch.from_numpy(x).to(DEV) for x in w]
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_prep_qkv_golden(dtype):
+    z = np.load(os.path.join(G, "prepare_qkv_fp32.npz"))
+    H, pph, ppw, ns = 2, 3, 4, 6
+    w, wd = _norm_params(7)
+    tol = dict(max_abs=3e-2, cos=0.9999)
+    for f in (0, 5, 41):
+        qkv = z[f"rope3d_f{f}_qkv"]
+        src = torch.from_numpy(qkv).to(DEV) if dtype == "f32" else bf(qkv)
+        cs = P.ops.rope3d_table(f, pph, ppw, ns, DEV)
+        ang = O.rope3d_angles(f, pph, ppw, ns)
+        assert np.abs(cs[..., 0].cpu().numpy() - np.cos(ang)).max() < 1e-6
+        assert np.abs(cs[..., 1].cpu().numpy() - np.sin(ang)).max() < 1e-6
+        q, k, v = P.ops.prep_qkv(src, H, ns + pph * ppw, *wd, cs, _lib.ROPE_3D)
+        if dtype == "f32":   # reference result on the same fp32 input, rounded once to bf16
+            for got, key in ((q, "q"), (k, "k"), (v, "v")):
+                assert_close(got, z[f"rope3d_f{f}_{key}"].astype(np.float64), f"3d f={f} {key}", **tol)
+                ulp = np.abs(got.float().cpu().numpy() - O.bf16_round(z[f"rope3d_f{f}_{key}"]))
+                assert (ulp <= np.abs(z[f"rope3d_f{f}_{key}"]) * 2 ** -7 + 1e-6).all()
+        else:
+            wq, wk, wv = O.prepare_qkv(r(qkv), H, *w, rope="3d", f=f, pph=pph, ppw=ppw, num_special=ns)
+            for got, want, key in ((q, wq, "q"), (k, wk, "k"), (v, wv, "v")):
+                assert_close(got, want, f"3d bf16 f={f} {key}", **tol)
+    qkv = z["rope2d_qkv"]
+    cs = P.ops.rope2d_table(pph, ppw, ns, DEV)
+    q, k, v = P.ops.prep_qkv(torch.from_numpy(qkv).to(DEV), H, ns + pph * ppw, *wd, cs, _lib.ROPE_2D)
+    for got, key in ((q, "q"), (k, "k"), (v, "v")):
+        assert_close(got, z[f"rope2d_{key}"].astype(np.float64), f"2d {key}", **tol)
+
+
+def test_append_fused_equals_prep_then_append():
+    """Fused LayerNorm+RoPE+page write == prep_qkv followed by append_frame, bit for bit, incl. a special
+    run that straddles two special pages."""
+    H, pph, ppw, ns = 2, 3, 4, 6
+    tpf = ns + pph * ppw                      # 18 tokens, page 12: specials straddle at frame 2 (12 = 2*6), 3...
+    w, wd = _norm_params(3)
+    kw = dict(device=DEV, scale_frames=1, sliding_window=2, max_total_frames=30)
+    a = P.B200KVCacheManager(1, 19, tpf, H, 64, **kw)
+    b = P.B200KVCacheManager(1, 19, tpf, H, 64, **kw)
+    a2 = P.B200KVCacheManager(1, 19, 11, H, 64, num_special_tokens=4, **kw)   # page 7, 4 specials: 7 % 4 != 0
+    b2 = P.B200KVCacheManager(1, 19, 11, H, 64, num_special_tokens=4, **kw)
+    for t in range(9):
+        qkv = torch.from_numpy(seeded.randn(40 + t, tpf, 3 * H * 64)).to(DEV)
+        cs = P.ops.rope3d_table(t, pph, ppw, ns, DEV)
+        q1 = a.append_frame_fused(0, qkv, *wd, cs, _lib.ROPE_3D)
+        q2, k2, v2 = P.ops.prep_qkv(qkv, H, tpf, *wd, cs, _lib.ROPE_3D)
+        b.append_frame(0, k2, v2)
+        for m in (a, b):
+            m.evict_frames(0, 1, 2)
+        assert torch.equal(q1, q2)
+        assert torch.equal(a.kv_caches[0], b.kv_caches[0])
+        # geometry whose specials straddle pages (no rope: the table is sized for tpf tokens)
+        qkv = torch.from_numpy(seeded.randn(80 + t, 11, 3 * H * 64)).to(DEV)
+        q1 = a2.append_frame_fused(0, qkv, *wd, None, _lib.ROPE_NONE)
+        q2, k2, v2 = P.ops.prep_qkv(qkv, H, 11, *wd, None, _lib.ROPE_NONE)
+        b2.append_frame(0, k2, v2)
+        for m in (a2, b2):
+            m.evict_frames(0, 1, 2)
+        assert torch.equal(q1, q2) and torch.equal(a2.kv_caches[0], b2.kv_caches[0])
+    assert a.device_status() == 0 and a2.device_status() == 0
+    # straddle really happened: 9 frames * 4 specials = 36 tokens over pages of 7
+    assert len(a2.all_special_pages[0]) == 6 and a2.compute_last_page_len(0) == 1
+
+
+# ---------------------------------------------------------------- production geometry
+def test_full_geometry_properties():
+    """378x518 geometry: 1005 tokens/frame, 16 heads, page 999, scale 8 + window 64, 80 keyframes.
+    Checked through size-independent properties and the oracle on a sample of (head, query) pairs."""
+    tpf, H = 1005, 16
+    m = P.B200KVCacheManager(1, 88, tpf, H, 64, device=DEV, max_total_frames=400)
+    gen = torch.Generator(device=DEV).manual_seed(2)
+    for t in range(80):
+        k = torch.randn(tpf, H, 64, device=DEV, generator=gen)
+        v = torch.randn(tpf, H, 64, device=DEV, generator=gen)
+        m.append_frame(0, k, v.to(torch.bfloat16))
+        m.evict_frames(0, 8, 64)
+    assert m.get_cache_stats(0) == {"frame_count": 80, "scale_pages": 8, "live_pages": 64, "free_pages": 16,
+                                    "special_tokens": 480}
+    q = torch.randn(tpf, H, 64, device=DEV, generator=gen).to(torch.bfloat16)
+    out, lse = m.compute_attention(0, q, return_lse=True)
+    kk, vv = m._gather_kv(0)
+    assert kk.shape[0] == 999 * 72 + 480
+    # oracle on a sample of heads and query rows
+    rows = [0, 1, 127, 128, 500, 895, 896, 1004]
+    for h in (0, 7, 15):
+        want, wl = O.attention(q[rows][:, h:h + 1].float().cpu().numpy(), kk[:, h:h + 1].float().cpu().numpy(),
+                               vv[:, h:h + 1].float().cpu().numpy())
+        assert_close(out[rows][:, h:h + 1], want, f"full head {h}")
+        assert np.abs(lse[rows][:, h].cpu().numpy() - wl[:, 0]).max() < 2e-3
+    # property: V := 1 everywhere -> output == 1 (softmax weights sum to one)
+    m.kv_caches[0][:, 1] = 1.0
+    ones = m.compute_attention(0, q)
+    assert float((ones.float() - 1.0).abs().max()) < 1e-2
+    # property: the merge of two disjoint page ranges equals the single pass
+    m.kv_caches[0][:, 1] = m.kv_caches[0][:, 0] * 0.5     # some non-trivial V again
+    full = m.compute_attention(0, q)
+    n = len(m.build_visible_page_table(0))
+    parts, lses = [], []
+    for lo, hi in ((0, 30), (30, n)):
+        m.plan(lo, hi)
+        o, l = m.compute_attention_partial(0, q)
+        parts.append(o)
+        lses.append(l)
+    merged = P.ops.lse_merge(torch.stack(parts), torch.stack(lses))
+    assert float((merged.float() - full.float()).abs().max()) < 1e-2
+    assert cosine64(merged.float().cpu().numpy(), full.float().cpu().numpy()) > 0.99999
+    assert m.device_status() == 0
