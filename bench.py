@@ -1,0 +1,387 @@
+#!/usr/bin/env python
+"""Benchmark of the GCT streaming attention hot path on B200.
+
+One "step" = one streaming frame at 518x378 (1005 tokens, 16 heads x 64) through the hot path of all 24
+aggregator layers, at the steady state of a 10,000-frame sequence (8 anchor + 64 window frames of full
+tokens + 6 memory tokens of every past frame = 131,928 visible KV tokens):
+    frame block  : q/k LayerNorm + 2-D RoPE + bf16 cast  ->  dense attention 1005 x 1005
+    global block : fused q/k LayerNorm + 3-D RoPE + bf16 K/V page append -> eviction -> paged attention
+                   over the visible page table (split-KV + log-sum-exp merge)
+The qkv/proj Linear layers, MLPs, DINOv2 and the heads are outside the measured path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--mode streams|kvsplit]
+
+Prints ONE JSON line.  N > 1 is launched with torch.distributed.run, one rank per GPU:
+`streams` (default) runs one independent stream per GPU (weak scaling, no data-path collective);
+`kvsplit` shards one stream's visible pages over the GPUs and merges partial outputs with NCCL.
+`--impl reference` times the CPU port of the reference's SDPA streaming path on the host cores.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+TPF, HEADS, HEAD_DIM, DEPTH = 1005, 16, 64, 24
+PPH, PPW, NSPECIAL = 27, 37, 6
+SCALE_FRAMES, WINDOW = 8, 64
+METRIC = "streaming frames/s @518x378 bf16 (steady state, 10k-frame KV); attn % of TC peak"
+UNIT = "frames/s"
+
+
+def visible_kv(n_cached):
+    return (TPF - NSPECIAL) * min(n_cached, SCALE_FRAMES + WINDOW) + NSPECIAL * n_cached
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"bf16_tflops": d["bf16_tflops_sustained"], "hbm_gbs": d["hbm_gbs"], "which": "measured (sustained)"}
+    return {"bf16_tflops": 1400.0, "hbm_gbs": 6650.0, "which": "fallback"}
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.rows, self.proc, self.thread = [], None, None
+        try:
+            uuid = "GPU-" + str(torch.cuda.get_device_properties(device).uuid)
+            self.cmd = ["nvidia-smi", "-i", uuid, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                        "-lms", "200"]
+        except Exception:
+            self.cmd = None
+
+    def start(self):
+        if self.cmd is None:
+            return
+        try:
+            self.proc = subprocess.Popen(self.cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                self.rows.append([x.strip() for x in line.split(",")])
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        time.sleep(0.25)
+        self.proc.terminate()
+        self.thread.join(timeout=2)
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v == "Active":
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- workload (GPU arm)
+class HotPath:
+    """State of one stream on one GPU: cache manager at the n_cached-frame steady state + synthetic inputs."""
+
+    def __init__(self, device, n_cached, extra_frames, seed, shard=None):
+        import lingbot_map_b200 as P
+        from lingbot_map_b200 import _lib
+        self.P, self.lib, self.dev = P, _lib, device
+        self.shard = shard                      # (rank, world) for kvsplit, else None
+        g = torch.Generator(device=device).manual_seed(seed)
+        self.mgr = P.B200KVCacheManager(DEPTH, SCALE_FRAMES + WINDOW + 16, TPF, HEADS, HEAD_DIM, device=device,
+                                        scale_frames=SCALE_FRAMES, sliding_window=WINDOW,
+                                        max_total_frames=n_cached + extra_frames + 100)
+        for pool in self.mgr.kv_caches:         # cached K/V ~ N(0,1): logits q.k/8 have unit variance
+            pool.normal_(generator=g)
+        for b in range(DEPTH):                  # bookkeeping only: the pages already hold data
+            for _ in range(n_cached):
+                self.mgr.append_frame_bookkeeping(b)
+                self.mgr.evict_frames(b, SCALE_FRAMES, WINDOW)
+        C = HEADS * HEAD_DIM
+        rn = lambda *s: torch.randn(*s, device=device, generator=g)
+        self.qkv_frame = [rn(TPF, 3 * C).to(torch.bfloat16) for _ in range(DEPTH)]
+        self.qkv_global = [rn(TPF, 3 * C).to(torch.bfloat16) for _ in range(DEPTH)]
+        self.norm = [[1 + 0.1 * rn(64), 0.1 * rn(64), 1 + 0.1 * rn(64), 0.1 * rn(64)] for _ in range(2 * DEPTH)]
+        self.cs2d = P.ops.rope2d_table(PPH, PPW, NSPECIAL, device)
+        self.cs3d = torch.empty(TPF, 32, 2, dtype=torch.float32, device=device)
+        self.frame_index = n_cached
+        self.outs = [None] * (2 * DEPTH)
+        self.launches = 0
+
+    def step(self, qkv_frame=None, qkv_global=None):
+        P, lib, m = self.P, self.lib, self.mgr
+        qkv_frame = qkv_frame or self.qkv_frame
+        qkv_global = qkv_global or self.qkv_global
+        # 3-D RoPE table of this frame; the reference keeps time indices below max_frame_num, so wrap
+        P.ops.rope3d_table(self.frame_index % 1024, PPH, PPW, NSPECIAL, self.dev, out=self.cs3d)
+        self.launches += 1
+        for b in range(DEPTH):
+            q, k, v = P.ops.prep_qkv(qkv_frame[b], HEADS, TPF, *self.norm[2 * b], self.cs2d, lib.ROPE_2D)
+            self.outs[2 * b] = P.ops.dense_attention(q[None], k[None], v[None])
+            qg = m.append_frame_fused(b, qkv_global[b], *self.norm[2 * b + 1], self.cs3d, lib.ROPE_3D)
+            m.evict_frames(b, SCALE_FRAMES, WINDOW)
+            if self.shard is None:
+                self.outs[2 * b + 1] = m.compute_attention(b, qg)
+                self.launches += 5          # prep, dense attention, fused append, paged attention, merge
+            else:
+                from lingbot_map_b200 import distributed as D
+                self.outs[2 * b + 1] = D.sharded_attention(m, b, qg, *self.shard)
+                self.launches += 6          # ... + the cross-rank merge
+        self.frame_index += 1
+
+
+def run_gpu(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch N>1 with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    kvsplit = args.mode == "kvsplit" and world > 1
+    extra = args.steps + args.warmup + 8 + args.e2e_steps
+    hp = HotPath(dev, args.frames_cached, extra, seed=100 + (0 if kvsplit else rank),
+                 shard=(rank, world) if kvsplit else None)
+    m = hp.mgr
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        hp.step()
+    barrier()
+    assert m.device_status() == 0
+    # ---- timed region: device-resident inputs ----
+    m.kernel_timing(args.steps * DEPTH)
+    m.kernel_time()
+    sampler = ClockSampler(dev)
+    sampler.start()
+    launches0 = hp.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        hp.step()
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    clocks = sampler.stop()
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    total_ms = float(ms.item())
+    attn_ms, attn_launches = m.kernel_time()
+    m.kernel_timing(0)
+    gpu_launches = hp.launches - launches0
+    assert m.device_status() == 0 and hp.P.ops.device_status(dev) == 0
+    n_cached_now = m.num_frames
+    kv_now = visible_kv(n_cached_now)
+
+    # ---- end to end: host buffers in, host buffers out, copies inside the timed region ----
+    C3 = 3 * HEADS * HEAD_DIM
+    h_in_f = [t.cpu().pin_memory() for t in hp.qkv_frame]
+    h_in_g = [t.cpu().pin_memory() for t in hp.qkv_global]
+    h_out = [torch.empty(TPF, HEADS, HEAD_DIM, dtype=torch.bfloat16).pin_memory() for _ in range(2 * DEPTH)]
+    d_in_f = [torch.empty(TPF, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)]
+    d_in_g = [torch.empty(TPF, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)]
+
+    def e2e_step():
+        for b in range(DEPTH):
+            d_in_f[b].copy_(h_in_f[b], non_blocking=True)
+            d_in_g[b].copy_(h_in_g[b], non_blocking=True)
+        hp.step(d_in_f, d_in_g)
+        for i in range(2 * DEPTH):
+            h_out[i].copy_(hp.outs[i].view(TPF, HEADS, HEAD_DIM), non_blocking=True)
+
+    e2e_step()
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    t1.record()
+    barrier()
+    e2e_ms = torch.tensor([t0.elapsed_time(t1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    streams = 1 if kvsplit else world
+    e2e_fps = streams * args.e2e_steps / (float(e2e_ms.item()) / 1e3)
+    h2d = 2 * DEPTH * TPF * C3 * 2
+    d2h = 2 * DEPTH * TPF * HEADS * HEAD_DIM * 2
+
+    if rank == 0:
+        peaks = load_peaks()
+        flops = 4.0 * TPF * kv_now * HEAD_DIM * HEADS
+        kern_s = attn_ms / max(attn_launches, 1) / 1e3
+        achieved = flops / kern_s / 1e12 if attn_launches else None
+        line = {
+            "metric": METRIC, "value": streams * args.steps / (total_ms / 1e3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "strong" if kvsplit else "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "GCT hot path, 24 layers x (frame attention 1005x1005 + fused K/V append + paged "
+                                   f"global attention), 518x378, {n_cached_now} cached frames, kv={kv_now} tokens, "
+                                   "page 999, scale 8 + window 64, keyframe_interval 1",
+                       "parallelism": ("kv-pages sharded over %d GPUs, NCCL all-gather + LSE merge" % world) if kvsplit
+                       else ("%d independent stream(s), one per GPU" % world),
+                       "l2": "inputs larger than L2 (each layer streams 540 MB of K/V)",
+                       "clock_samples": clocks.get("samples")},
+            "clocks": {k: clocks.get(k) for k in ("sm_mhz", "sm_max_mhz", "reasons")},
+            "e2e": {"value": e2e_fps, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": args.e2e_steps},
+            "gpu_launches": gpu_launches,
+            "roofline": {"bound": "tensor", "kernel": "gct_attn_kernel<2> (paged global attention)",
+                         "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": (achieved / peaks["bf16_tflops"]) if achieved else None,
+                         "peak_source": peaks["which"], "kernel_us": kern_s * 1e6, "launches_timed": attn_launches,
+                         "flops_per_launch": flops, "attn_share_of_step": attn_ms / total_ms,
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(max_seconds=25.0)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the paged attention kernel, from the
+# ncu capture summarised under profiles/ (None until a capture exists).
+NCU_DRAM_BYTES_PER_LAUNCH = None
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_layer_sample(n_cached, threads):
+    """One global layer + one frame layer of one streaming frame with the CPU port of the reference's SDPA
+    path, at the n_cached-frame steady state.  Returns seconds for the pair."""
+    from oracle import sdpa_port as SP
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(1)
+    C = HEADS * HEAD_DIM
+    rn = lambda *s: torch.randn(*s, generator=g)
+    params = {"qkv.weight": None, "qkv.bias": None, "proj.weight": None, "proj.bias": None,
+              "q_norm.weight": 1 + 0.1 * rn(64), "q_norm.bias": 0.1 * rn(64),
+              "k_norm.weight": 1 + 0.1 * rn(64), "k_norm.bias": 0.1 * rn(64)}
+    port = SP.SdpaStreamPort(params, HEADS, SCALE_FRAMES, WINDOW, NSPECIAL)
+    # steady state of the dict cache: 72 full frames + specials of the evicted ones (attention.py:676-718)
+    port.k = rn(1, HEADS, SCALE_FRAMES + WINDOW, TPF, HEAD_DIM)
+    port.v = rn(1, HEADS, SCALE_FRAMES + WINDOW, TPF, HEAD_DIM)
+    n_ev = max(n_cached - SCALE_FRAMES - WINDOW, 0)
+    port.k_special = rn(1, HEADS, n_ev, NSPECIAL, HEAD_DIM)
+    port.v_special = rn(1, HEADS, n_ev, NSPECIAL, HEAD_DIM)
+    qkv = rn(1, TPF, 3 * C)
+    cos, sin = SP.rope3d_cos_sin(n_cached % 1024, 1, PPH, PPW, NSPECIAL)
+    import torch.nn.functional as F
+
+    def split(t):
+        q, k, v = t.reshape(1, TPF, 3, HEADS, HEAD_DIM).permute(2, 0, 3, 1, 4).unbind(0)
+        q = F.layer_norm(q, (HEAD_DIM,), params["q_norm.weight"], params["q_norm.bias"], 1e-5)
+        k = F.layer_norm(k, (HEAD_DIM,), params["k_norm.weight"], params["k_norm.bias"], 1e-5)
+        return q, k, v
+
+    t0 = time.perf_counter()
+    with torch.no_grad():
+        q, k, v = split(qkv)                                    # global layer (attention.py:601-670, minus Linears)
+        q, k = SP.apply_rope3d(q, cos, sin), SP.apply_rope3d(k, cos, sin)
+        port.attend(q, k, v, 1)
+        q, k, v = split(qkv)                                    # frame layer (attention.py:65-84, minus Linears)
+        q, k = SP.apply_rope3d(q, cos, sin), SP.apply_rope3d(k, cos, sin)   # same cost as the 2-D rotation
+        F.scaled_dot_product_attention(q, k, v)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(max_seconds=25.0, n_cached=10000):
+    threads = os.cpu_count() or 1
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < 3 and (not times or time.perf_counter() - t_start + times[-1] < max_seconds):
+        times.append(cpu_layer_sample(n_cached, threads))
+    best = min(times)
+    return {"value": 1.0 / (DEPTH * best), "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"1 of {DEPTH} layer pairs (global attention over kv={visible_kv(n_cached + 1)} fp32 with the "
+                      f"reference's dict cache cat/evict/clone + frame attention 1005x1005), best of {len(times)}, "
+                      f"x{DEPTH} per frame; torch CPU SDPA, {threads} threads",
+            "seconds_per_sample": best}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    for _ in range(min(args.warmup, 1)):
+        cpu_layer_sample(args.frames_cached, threads)
+    steps = min(args.steps, 8)            # each step is a bounded sample: 1 of 24 layer pairs
+    t = [cpu_layer_sample(args.frames_cached, threads) for _ in range(steps)]
+    per_frame = DEPTH * (sum(t) / len(t))
+    value = 1.0 / per_frame
+    cb = {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+          "sample": f"each step = 1 of {DEPTH} layer pairs at kv={visible_kv(args.frames_cached + 1)}, x{DEPTH}; "
+                    f"{steps} steps timed (capped at 8 to stay within minutes)"}
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": min(args.warmup, 1), "ms_per_step": per_frame * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "CPU port of the reference's SDPA streaming path (oracle/sdpa_port.py), same frame "
+                               f"geometry and {args.frames_cached}-frame cache state as the GPU arm", "cores": threads},
+        "cpu_baseline": cb,
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--mode", default="streams", choices=["streams", "kvsplit"])
+    ap.add_argument("--frames-cached", type=int, default=10000)
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=24,
+                    help="aggregator depth; the metric is defined at 24, smaller values are for profiler captures")
+    args = ap.parse_args()
+    global DEPTH
+    DEPTH = args.layers
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU path for the product")
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

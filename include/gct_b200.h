@@ -139,6 +139,11 @@ int gct_mgr_attention_partial(gct_mgr_t* m, int block, const void* q_dev, int q_
 
 /* Reads the device status word (blocks on `stream`): 0 if no kernel reported a problem. */
 int gct_mgr_device_status(gct_mgr_t* m, void* stream, int* status_out);
+/* Measurement aid (no counterpart in the reference): bracket every launch of the attention kernel
+ * with a CUDA-event pair on the launching stream, for up to max_launches launches (0 switches it
+ * off); gct_mgr_kernel_time waits for them, returns the summed kernel time and rearms the events. */
+int gct_mgr_kernel_timing(gct_mgr_t* m, int max_launches);
+int gct_mgr_kernel_time(gct_mgr_t* m, double* total_ms_out, int* launches_out);
 /* Number of kernels this manager has launched since creation. */
 int gct_mgr_launch_count(const gct_mgr_t* m, int64_t* count_out);
 

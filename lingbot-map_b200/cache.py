@@ -299,6 +299,17 @@ class B200KVCacheManager:
         self._check(self._lib.gct_mgr_device_status(self._handle, _stream_ptr(self.device), C.byref(st)))
         return st.value
 
+    def kernel_timing(self, max_launches: int) -> None:
+        """Time every attention-kernel launch with a CUDA-event pair (0 = off); see kernel_time()."""
+        self._require_device()
+        self._check(self._lib.gct_mgr_kernel_timing(self._handle, max_launches))
+
+    def kernel_time(self):
+        """(total milliseconds, launches) of the attention kernel since the last call; synchronises."""
+        ms, n = C.c_double(), C.c_int()
+        self._check(self._lib.gct_mgr_kernel_time(self._handle, C.byref(ms), C.byref(n)))
+        return ms.value, n.value
+
     @property
     def launch_count(self) -> int:
         n = C.c_int64()

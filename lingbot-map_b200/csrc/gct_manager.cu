@@ -103,6 +103,10 @@ struct gct_mgr {
   int tmq_nq = 0;
   CUtensorMap tm_q{};
   int64_t launches = 0;
+  // optional CUDA-event timing of the attention kernel alone (gct_mgr_kernel_timing)
+  bool timing = false;
+  std::vector<cudaEvent_t> ev_start, ev_stop;
+  size_t ev_used = 0;
 };
 
 static constexpr size_t kWsHeader = 4096;      // status word
@@ -138,6 +142,8 @@ static WsLayout ws_layout(const gct_mgr* m) {
   return w;
 }
 
+static int check_bound_fwd(const gct_mgr* m);
+
 extern "C" {
 
 const char* gct_last_error(void) { return g_last_error.c_str(); }
@@ -169,7 +175,47 @@ int gct_mgr_create(gct_mgr_t** out, const gct_mgr_config_t* cfg, gct_mgr_geometr
 }
 
 int gct_mgr_destroy(gct_mgr_t* m) {
+  if (m != nullptr) {
+    for (cudaEvent_t e : m->ev_start) cudaEventDestroy(e);
+    for (cudaEvent_t e : m->ev_stop) cudaEventDestroy(e);
+  }
   delete m;
+  return GCT_OK;
+}
+
+int gct_mgr_kernel_timing(gct_mgr_t* m, int max_launches) {
+  int rc = check_bound_fwd(m);
+  if (rc != GCT_OK) return rc;
+  for (cudaEvent_t e : m->ev_start) cudaEventDestroy(e);
+  for (cudaEvent_t e : m->ev_stop) cudaEventDestroy(e);
+  m->ev_start.clear();
+  m->ev_stop.clear();
+  m->ev_used = 0;
+  m->timing = max_launches > 0;
+  for (int i = 0; i < max_launches; ++i) {
+    cudaEvent_t a, b;
+    GCT_CUDA_CHECK(cudaEventCreate(&a));
+    GCT_CUDA_CHECK(cudaEventCreate(&b));
+    m->ev_start.push_back(a);
+    m->ev_stop.push_back(b);
+  }
+  return GCT_OK;
+}
+
+int gct_mgr_kernel_time(gct_mgr_t* m, double* total_ms_out, int* launches_out) {
+  int rc = check_bound_fwd(m);
+  if (rc != GCT_OK) return rc;
+  if (total_ms_out == nullptr || launches_out == nullptr) return fail(GCT_ERR_INVALID, "null argument");
+  double total = 0.0;
+  for (size_t i = 0; i < m->ev_used; ++i) {
+    GCT_CUDA_CHECK(cudaEventSynchronize(m->ev_stop[i]));
+    float ms = 0.f;
+    GCT_CUDA_CHECK(cudaEventElapsedTime(&ms, m->ev_start[i], m->ev_stop[i]));
+    total += ms;
+  }
+  *total_ms_out = total;
+  *launches_out = static_cast<int>(m->ev_used);
+  m->ev_used = 0;
   return GCT_OK;
 }
 
@@ -282,6 +328,9 @@ static int check_bound(const gct_mgr* m) {
   if (!m->bound) return fail(GCT_ERR_INVALID, "manager has no device memory bound (gct_mgr_bind)");
   return GCT_OK;
 }
+}  // extern "C"
+static int check_bound_fwd(const gct_mgr* m) { return check_bound(m); }
+extern "C" {
 
 static void fill_paged_dst(const gct_mgr* m, int block, const AppendPlan& pl, PrepLaunch* p) {
   p->pool = m->pools[block];
@@ -488,6 +537,18 @@ int gct_mgr_plan(gct_mgr_t* m, int page_begin, int page_end, void* stream) {
   return GCT_OK;
 }
 
+// Launch the attention kernel, bracketed by a CUDA-event pair when kernel timing is on.
+static int timed_attention(gct_mgr* m, const AttnLaunch& a, cudaStream_t stream) {
+  const bool t = m->timing && m->ev_used < m->ev_start.size();
+  if (t) GCT_CUDA_CHECK(cudaEventRecord(m->ev_start[m->ev_used], stream));
+  const int rc = launch_attention(a, stream);
+  if (t) {
+    GCT_CUDA_CHECK(cudaEventRecord(m->ev_stop[m->ev_used], stream));
+    m->ev_used += 1;
+  }
+  return rc;
+}
+
 static int run_paged(gct_mgr* m, int block, const void* q_dev, int q_dtype, int n_q, __nv_bfloat16* out_bf16,
                      float* out_f32, float* lse_dev, cudaStream_t stream) {
   int rc = check_bound(m);
@@ -536,13 +597,13 @@ static int run_paged(gct_mgr* m, int block, const void* q_dev, int q_dtype, int 
     a.final_bf16 = true;
     a.out = out_bf16;
     m->launches += 1;
-    return launch_attention(a, stream);
+    return timed_attention(m, a, stream);
   }
   a.final_bf16 = false;
   a.part_o = m->part_o;
   a.part_lse = m->part_lse;
   // partial rows are laid out with n_q rows per split
-  rc = launch_attention(a, stream);
+  rc = timed_attention(m, a, stream);
   if (rc != GCT_OK) return rc;
   m->launches += 2;
   return launch_merge(m->part_o, m->part_lse, a.splits, rows, out_bf16, out_f32, lse_dev, stream);
