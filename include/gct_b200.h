@@ -179,6 +179,24 @@ int gct_rope2d_table(int pph, int ppw, int num_special, float base, float* cs_ou
 int gct_lse_merge(const float* parts_dev, const float* lse_dev, int groups, int n_q, int heads, void* out_dev,
                   float* lse_out_dev, void* stream);
 
+/* Paged attention that allocates nothing (this entry point has no counterpart in the reference).
+ * For hosts that cannot call cudaMalloc - e.g. a process that gave all device memory to its own pool
+ * at start-up, or a loop that cannot afford cudaMalloc's device-wide synchronisation - and therefore
+ * cannot provide the workspace gct_mgr_attention needs.  Same computation as gct_mgr_attention over the
+ * pages `visible_pages_host[0..n_pages)` of one block's pool [max_num_pages, 2, page_size, heads, 64]
+ * bf16; q_dev and out_dev are [n_q, heads, 64] bf16.  The scratch (device page table, split-KV
+ * partials, status word) is a fixed array inside the library image, about 17 MB on every GPU that
+ * loads the library, held until the process exits.
+ * Limits: n_q * heads <= 16384, n_pages <= 4096 (GCT_ERR_CAPACITY beyond), at most 4 KV splits.
+ * The first call on a device looks up the array's address on that device (cudaGetSymbolAddress); make
+ * that first call before any stream capture begins.  All calls on a GPU share the array: calls whose
+ * GPU work can overlap (several streams or host threads) race and must be serialised by the caller.
+ * device_status_out may be NULL; otherwise the call synchronises `stream` and stores the kernels'
+ * status word (0 = ok). */
+int gct_attn_paged_static(const void* pool_dev, int max_num_pages, int page_size, int heads,
+                          const int32_t* visible_pages_host, int n_pages, int last_page_len, const void* q_dev,
+                          int n_q, void* out_dev, void* stream, int* device_status_out);
+
 #ifdef __cplusplus
 }
 #endif
