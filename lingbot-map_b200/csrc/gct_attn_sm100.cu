@@ -5,26 +5,26 @@
 //
 // One CTA owns QT (1 or 2) query tiles of 128 rows of one head and one contiguous range of KV blocks
 // (128 tokens each).  Warp roles:
-//   warps [0, 4*QT)   softmax: one thread per query row; warp w reads TMEM lanes 32*(w%4)..+31
-//   warp  4*QT        producer: TMA loads of Q once and of K/V blocks into a 3-stage ring
-//   warp  4*QT+1      MMA issuer: tcgen05.mma  S = Q K^T (128x128x64)  and  PV = P V (128x64x128)
-// TMEM columns: S tile t at [128 t, 128 t + 128), PV tile t at [128 QT + 64 t, +64).
-// Per KV block j and tile t:
-//   MMA:      S_j -> commit s_full[t]
-//   softmax:  wait s_full; row max; (wait pv_full of block j-1; O = O*alpha + PV_{j-1});
-//             P = exp2(S*c - m*c) as bf16 into swizzled smem; arrive p_full[t]
-//   MMA:      wait p_full; issue S_{j+1}; issue PV_j = P V_j -> commit pv_full[t];
-//             after the last tile commit kv_empty[stage]
-// The running output stays in registers (64 fp32 per row); every mbarrier wait is bounded and
-// reports through the status word instead of spinning forever.
+//   warps [0, 4*QT)        softmax: one thread per query row; warp w owns TMEM lanes 32*(w%4)..+31
+//   warp  4*QT             producer: TMA loads of Q once, then K and V blocks into two 4-stage rings
+//   warps 4*QT+1 .. +QT    MMA issuers, one per query tile: tcgen05.mma
+//                              S  = Q K^T   (M128 N128 K64,  A and B from shared memory)
+//                              O += P V     (M128 N64  K128, A = P from TMEM, B = V from shared memory)
+// TMEM columns (fp32): S_t at [128t, +128), O_t at [128QT + 64t, +64), P_t (bf16 pairs) at [192QT + 64t, +64).
+// Per KV block j of tile t:
+//   softmax   wait s_full; copy the S row into 128 registers; arrive s_empty  -> S_{j+1} may overwrite S
+//             row max; the reference maximum only moves when the row max grows by more than 2^8
+//             (then O is rescaled in TMEM, which is rare after the first blocks);
+//             P = exp2(S*c - m*c) as bf16 pairs into TMEM; arrive p_full
+//   MMA       wait s_empty, K_{j+1}: issue S_{j+1} (runs under the softmax of block j) -> s_full, k_empty
+//             wait p_full,  V_j    : issue O += P_j V_j                                -> pv_full, v_empty
+// Every mbarrier wait is bounded and reports through the status word instead of spinning forever.
 #include "gct_common.h"
 
 namespace gct {
 namespace {
 
-constexpr int kStages = 3;
 constexpr uint32_t kTileBytes = 128 * 64 * 2;      // one 128x64 bf16 tile, 128B-swizzled
-constexpr uint32_t kPBytes = 2 * kTileBytes;       // P tile 128x128 bf16 = two K-halves
 constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at 2 GHz; only reached on a bug
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -142,10 +142,39 @@ constexpr uint32_t kIdescS = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) <
 constexpr uint32_t kIdescPV =
     (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
 
+// D[tmem] (+)= A[tmem] * B[smem]: A is read from TMEM (lane = row, two bf16 per 32-bit column).
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 32 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;
@@ -164,21 +193,30 @@ struct KernelArgs {
   int* status;
 };
 
+constexpr int kKStages = 4;
+constexpr int kVStages = 4;
+constexpr float kRescaleThreshold = 8.0f;   // in log2 units of the scaled logits
+
 template <int QT>
 struct SmemLayout {
   static constexpr uint32_t q_off = 0;
   static constexpr uint32_t k_off = q_off + QT * kTileBytes;
-  static constexpr uint32_t v_off = k_off + kStages * kTileBytes;
-  static constexpr uint32_t p_off = v_off + kStages * kTileBytes;
-  static constexpr uint32_t bar_off = p_off + QT * kPBytes;
-  // barriers: q_full, k_full[ST], v_full[ST], kv_empty[ST], s_full[QT], p_full[QT], pv_full[QT]
-  static constexpr int n_bars = 1 + 3 * kStages + 3 * QT;
+  static constexpr uint32_t v_off = k_off + kKStages * kTileBytes;
+  static constexpr uint32_t bar_off = v_off + kVStages * kTileBytes;
+  // barriers: q_full, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], then per tile s_full, s_empty, p_full, pv_full
+  static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 4 * QT;
   static constexpr uint32_t misc_off = bar_off + n_bars * 8;
   static constexpr uint32_t total = misc_off + 16;
 };
 
+// Threads per CTA: the softmax warpgroups plus one control warpgroup slot (producer + QT MMA warps; at
+// QT == 2 a fourth, idle warp completes the warpgroup so that registers can be moved between
+// warpgroups with setmaxnreg).
 template <int QT>
-__global__ void __launch_bounds__(QT * 128 + 64, 1)
+constexpr int kThreads = (QT == 2) ? 384 : 192;
+
+template <int QT>
+__global__ void __launch_bounds__(kThreads<QT>, 1)
 gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const KernelArgs a) {
   using L = SmemLayout<QT>;
@@ -188,19 +226,24 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t bars = sbase + L::bar_off;
   auto bar_q_full = [&]() { return bars; };
   auto bar_k_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto bar_v_full = [&](int s) { return bars + 8u * (1 + kStages + s); };
-  auto bar_kv_empty = [&](int s) { return bars + 8u * (1 + 2 * kStages + s); };
-  auto bar_s_full = [&](int t) { return bars + 8u * (1 + 3 * kStages + t); };
-  auto bar_p_full = [&](int t) { return bars + 8u * (1 + 3 * kStages + QT + t); };
-  auto bar_pv_full = [&](int t) { return bars + 8u * (1 + 3 * kStages + 2 * QT + t); };
+  auto bar_k_empty = [&](int s) { return bars + 8u * (1 + kKStages + s); };
+  auto bar_v_full = [&](int s) { return bars + 8u * (1 + 2 * kKStages + s); };
+  auto bar_v_empty = [&](int s) { return bars + 8u * (1 + 2 * kKStages + kVStages + s); };
+  constexpr int kTileBars = 1 + 2 * kKStages + 2 * kVStages;
+  auto bar_s_full = [&](int t) { return bars + 8u * (kTileBars + 4 * t + 0); };
+  auto bar_s_empty = [&](int t) { return bars + 8u * (kTileBars + 4 * t + 1); };
+  auto bar_p_full = [&](int t) { return bars + 8u * (kTileBars + 4 * t + 2); };
+  auto bar_pv_full = [&](int t) { return bars + 8u * (kTileBars + 4 * t + 3); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::misc_off);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(smem + L::misc_off + 4);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   constexpr int kProducerWarp = 4 * QT;
-  constexpr int kMmaWarp = 4 * QT + 1;
+  constexpr int kFirstMmaWarp = 4 * QT + 1;
   constexpr uint32_t kTmemCols = (QT == 2) ? 512u : 256u;
+  constexpr uint32_t kOCol = 128u * QT;
+  constexpr uint32_t kPCol = 192u * QT;
 
   // ---- work coordinates ----
   int idx = blockIdx.x;
@@ -217,20 +260,24 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // ---- set-up ----
   if (threadIdx.x == 0) {
     mbar_init(bar_q_full(), 1);
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kKStages; ++s) {
       mbar_init(bar_k_full(s), 1);
+      mbar_init(bar_k_empty(s), QT);
+    }
+    for (int s = 0; s < kVStages; ++s) {
       mbar_init(bar_v_full(s), 1);
-      mbar_init(bar_kv_empty(s), 1);
+      mbar_init(bar_v_empty(s), QT);
     }
     for (int t = 0; t < QT; ++t) {
       mbar_init(bar_s_full(t), 1);
-      mbar_init(bar_p_full(t), 128);
+      mbar_init(bar_s_empty(t), 4);
+      mbar_init(bar_p_full(t), 4);
       mbar_init(bar_pv_full(t), 1);
     }
     *cta_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == kMmaWarp) {
+  if (warp == kFirstMmaWarp) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
   }
   if (warp == kProducerWarp && lane == 0) {
@@ -243,17 +290,17 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // QT == 2: 384 threads share 64K registers (168 each at launch); the control warpgroup gives most of its
+  // share to the two softmax warpgroups, whose threads hold a whole 128-column S row.
   if (warp == kProducerWarp) {
     // =========================== producer ===========================
+    if constexpr (QT == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
     if (lane == 0) {
       mbar_arrive_expect_tx(bar_q_full(), QT * kTileBytes);
       for (int t = 0; t < QT; ++t)
         tma_load_4d(sbase + L::q_off + t * kTileBytes, &tm_q, bar_q_full(), 0, h, (qg * QT + t) * kTileM, b);
       int page = b, cur_pi = -1;
       for (int j = 0; j < nblk; ++j) {
-        const int st = j % kStages;
-        const uint32_t ph = (j / kStages) & 1;
-        if (!mbar_wait(bar_kv_empty(st), ph ^ 1u, cta_abort, a.status)) break;
         const int g = g0 + j;
         const int pi = g / a.blocks_per_page;
         const int jb = g - pi * a.blocks_per_page;
@@ -261,186 +308,207 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           page = __ldg(a.page_table + pi);
           cur_pi = pi;
         }
-        mbar_arrive_expect_tx(bar_k_full(st), kTileBytes);
-        tma_load_4d(sbase + L::k_off + st * kTileBytes, &tm_k, bar_k_full(st), 0, h, jb * kBlockN, page);
-        mbar_arrive_expect_tx(bar_v_full(st), kTileBytes);
-        tma_load_4d(sbase + L::v_off + st * kTileBytes, &tm_v, bar_v_full(st), 0, h, jb * kBlockN, page);
+        const int ks = j % kKStages, vs = j % kVStages;
+        if (!mbar_wait(bar_k_empty(ks), ((j / kKStages) & 1) ^ 1u, cta_abort, a.status)) break;
+        mbar_arrive_expect_tx(bar_k_full(ks), kTileBytes);
+        tma_load_4d(sbase + L::k_off + ks * kTileBytes, &tm_k, bar_k_full(ks), 0, h, jb * kBlockN, page);
+        if (!mbar_wait(bar_v_empty(vs), ((j / kVStages) & 1) ^ 1u, cta_abort, a.status)) break;
+        mbar_arrive_expect_tx(bar_v_full(vs), kTileBytes);
+        tma_load_4d(sbase + L::v_off + vs * kTileBytes, &tm_v, bar_v_full(vs), 0, h, jb * kBlockN, page);
       }
     }
-  } else if (warp == kMmaWarp) {
-    // =========================== MMA issuer ===========================
-    if (lane == 0) {
-      auto issue_s = [&](int t, int st) {
+  } else if (warp >= kFirstMmaWarp) {
+    // =========================== MMA issuer of tile t ===========================
+    if constexpr (QT == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    const int t = warp - kFirstMmaWarp;
+    if (lane == 0 && t < QT) {
+      auto issue_s = [&](int ks) {
         const uint64_t ad = smem_desc(sbase + L::q_off + t * kTileBytes, 16, 1024);
-        const uint64_t bd = smem_desc(sbase + L::k_off + st * kTileBytes, 16, 1024);
+        const uint64_t bd = smem_desc(sbase + L::k_off + ks * kTileBytes, 16, 1024);
 #pragma unroll
         for (int k = 0; k < 4; ++k)   // 64 = 4 x K16; +32 B per step inside the 128 B swizzle row
           umma_ss(tmem_base + t * 128, ad + 2 * k, bd + 2 * k, kIdescS, k > 0);
       };
-      auto issue_pv = [&](int t, int st) {
+      auto issue_pv = [&](int vs, uint32_t accumulate) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {   // 128 tokens = 8 x K16
-          const uint64_t ad =
-              smem_desc(sbase + L::p_off + t * kPBytes + (k >> 2) * kTileBytes + (k & 3) * 32, 16, 1024);
-          const uint64_t bd = smem_desc(sbase + L::v_off + st * kTileBytes + k * 2048, 16, 1024);
-          umma_ss(tmem_base + QT * 128 + t * 64, ad, bd, kIdescPV, k > 0);
+        for (int k = 0; k < 8; ++k) {   // 128 tokens = 8 x K16: 8 TMEM columns of P and 16 V rows per step
+          const uint64_t bd = smem_desc(sbase + L::v_off + vs * kTileBytes + k * 2048, 16, 1024);
+          umma_ts(tmem_base + kOCol + t * 64, tmem_base + kPCol + t * 64 + k * 8, bd, kIdescPV,
+                  (k > 0) ? 1u : accumulate);
         }
       };
       bool ok = mbar_wait(bar_q_full(), 0, cta_abort, a.status) && mbar_wait(bar_k_full(0), 0, cta_abort, a.status);
       if (ok) {
         tc_fence_after();
-        for (int t = 0; t < QT; ++t) {
-          issue_s(t, 0);
-          tc_commit(bar_s_full(t));
-        }
+        issue_s(0);
+        tc_commit(bar_s_full(t));
+        tc_commit(bar_k_empty(0));
       }
       for (int j = 0; ok && j < nblk; ++j) {
-        const int st = j % kStages;
-        const uint32_t ph = (j / kStages) & 1;
-        for (int t = 0; t < QT; ++t) {
-          if (!(ok = mbar_wait(bar_p_full(t), j & 1, cta_abort, a.status))) break;
+        if (j + 1 < nblk) {
+          const int ks = (j + 1) % kKStages;
+          if (!(ok = mbar_wait(bar_s_empty(t), j & 1, cta_abort, a.status))) break;
+          if (!(ok = mbar_wait(bar_k_full(ks), ((j + 1) / kKStages) & 1, cta_abort, a.status))) break;
           tc_fence_after();
-          if (j + 1 < nblk) {
-            const int st1 = (j + 1) % kStages;
-            if (t == 0 && !(ok = mbar_wait(bar_k_full(st1), ((j + 1) / kStages) & 1, cta_abort, a.status))) break;
-            tc_fence_after();
-            issue_s(t, st1);
-            tc_commit(bar_s_full(t));
-          }
-          if (t == 0 && !(ok = mbar_wait(bar_v_full(st), ph, cta_abort, a.status))) break;
-          tc_fence_after();
-          issue_pv(t, st);
-          tc_commit(bar_pv_full(t));
+          issue_s(ks);
+          tc_commit(bar_s_full(t));
+          tc_commit(bar_k_empty(ks));
         }
-        if (ok) tc_commit(bar_kv_empty(st));
+        const int vs = j % kVStages;
+        if (!(ok = mbar_wait(bar_p_full(t), j & 1, cta_abort, a.status))) break;
+        if (!(ok = mbar_wait(bar_v_full(vs), (j / kVStages) & 1, cta_abort, a.status))) break;
+        tc_fence_after();
+        issue_pv(vs, j > 0 ? 1u : 0u);
+        tc_commit(bar_pv_full(t));
+        tc_commit(bar_v_empty(vs));
       }
     }
   } else {
     // =========================== softmax ===========================
+    if constexpr (QT == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     const int t = warp >> 2;                       // query tile of this warp
     const int row = ((warp & 3) << 5) | lane;      // row inside the tile == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) << 5) << 16;
     const uint32_t s_addr = tmem_base + lane_addr + t * 128;
-    const uint32_t pv_addr = tmem_base + lane_addr + QT * 128 + t * 64;
-    uint8_t* p_row = smem + L::p_off + t * kPBytes + row * 128;
-    const uint32_t sw = static_cast<uint32_t>(row & 7);
+    const uint32_t o_addr = tmem_base + lane_addr + kOCol + t * 64;
+    const uint32_t p_addr = tmem_base + lane_addr + kPCol + t * 64;
     const float c = a.scale_log2;
-    float o[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) o[i] = 0.f;
-    float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
+    float m = -INFINITY, l = 0.f;                   // m: reference maximum (raw logit units)
     bool ok = true;
-    uint32_t r[32];
+    uint32_t s[128];
 
     for (int j = 0; j < nblk; ++j) {
       if (!(ok = mbar_wait(bar_s_full(t), j & 1, cta_abort, a.status))) break;
       tc_fence_after();
+      {
+        uint32_t(&s0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
+        uint32_t(&s1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32]);
+        uint32_t(&s2)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[64]);
+        uint32_t(&s3)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[96]);
+        tmem_ld32(s_addr, s0);
+        tmem_ld32(s_addr + 32, s1);
+        tmem_ld32(s_addr + 64, s2);
+        tmem_ld32(s_addr + 96, s3);
+        tmem_wait_ld();
+      }
+      // the S tile is in registers: the tensor core may overwrite it with the next block
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_s_empty(t));
+
       // valid tokens of this block
       const int g = g0 + j;
       const int pi = g / a.blocks_per_page;
       const int jb = g - pi * a.blocks_per_page;
       const int plen = (pi == a.n_pages - 1) ? a.last_page_len : a.page_len;
       const int valid = min(kBlockN, plen - jb * kBlockN);
-
-      // pass 1: row maximum
-      float mx = m;
+      if (valid < kBlockN) {
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        tmem_ld32(s_addr + cc * 32, r);
-        tmem_wait_ld();
-        if (valid >= kBlockN) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (cc * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(r[i]));
-        }
+        for (int i = 0; i < 128; ++i)
+          if (i >= valid) s[i] = 0xff800000u;   // -inf: exp2 gives 0
       }
-      const float alpha = fast_exp2((m - mx) * c);   // m = -inf on the first block: exp2(-inf) = 0
-      // fold in the PV product of the previous block (it was computed against the previous maximum)
+
+      // row maximum, four independent chains of 3-input max
+      float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]), mx2 = __uint_as_float(s[2]),
+            mx3 = __uint_as_float(s[3]);
+#pragma unroll
+      for (int i = 4; i < 124; i += 8) {
+        mx0 = max3(mx0, __uint_as_float(s[i + 0]), __uint_as_float(s[i + 1]));
+        mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+        mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+        mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+      }
+      mx0 = max3(mx0, __uint_as_float(s[124]), __uint_as_float(s[125]));
+      mx1 = max3(mx1, __uint_as_float(s[126]), __uint_as_float(s[127]));
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      // move the reference maximum only when the row maximum outgrew it by more than 2^kRescaleThreshold;
+      // until then exponentials stay below 2^8 and every sum remains exact enough in fp32
+      float alpha = 1.f;
+      if ((mx - m) * c > kRescaleThreshold) {      // always true on the first block (m = -inf)
+        alpha = fast_exp2((m - mx) * c);           // exp2(-inf) = 0 on the first block
+        m = mx;
+      }
+      const float mc = m * c;
+
+      // P (and O) of this tile are free once the PV product of the previous block has completed
       if (j > 0) {
         if (!(ok = mbar_wait(bar_pv_full(t), (j - 1) & 1, cta_abort, a.status))) break;
         tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {   // rare: rescale this warp's 32 rows of O in TMEM
+          uint32_t ob[32];
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          tmem_ld32(pv_addr + hh * 32, r);
-          tmem_wait_ld();
+          for (int hh = 0; hh < 2; ++hh) {
+            tmem_ld32(o_addr + hh * 32, ob);
+            tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[hh * 32 + i] = fmaf(o[hh * 32 + i], alpha_prev, __uint_as_float(r[i]));
+            for (int i = 0; i < 32; ++i) ob[i] = __float_as_uint(__uint_as_float(ob[i]) * alpha);
+            tmem_st32(o_addr + hh * 32, ob);
+          }
         }
       }
-      // pass 2: P = exp2(S*c - m*c), row sum, bf16 into the swizzled P tile
-      const float mc = mx * c;
-      float rs = 0.f;
+
+      // P = exp2(S*c - m*c), row sum, bf16 pairs (two K values per 32-bit TMEM column)
+      float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        tmem_ld32(s_addr + cc * 32, r);
-        tmem_wait_ld();
-        float e[32];
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t pk[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = fast_exp2(fmaf(__uint_as_float(r[i]), c, -mc));
-          if (valid < kBlockN && cc * 32 + i >= valid) x = 0.f;
-          e[i] = x;
-          rs += x;
+        for (int i = 0; i < 32; i += 2) {
+          const float e0 = fast_exp2(fmaf(__uint_as_float(s[hh * 64 + 2 * i + 0]), c, -mc));
+          const float e1 = fast_exp2(fmaf(__uint_as_float(s[hh * 64 + 2 * i + 1]), c, -mc));
+          const float e2 = fast_exp2(fmaf(__uint_as_float(s[hh * 64 + 2 * i + 2]), c, -mc));
+          const float e3 = fast_exp2(fmaf(__uint_as_float(s[hh * 64 + 2 * i + 3]), c, -mc));
+          rs0 += e0;
+          rs1 += e1;
+          rs2 += e2;
+          rs3 += e3;
+          pk[i] = pack_bf16x2(e0, e1);
+          pk[i + 1] = pack_bf16x2(e2, e3);
         }
-        // columns [32cc, 32cc+32): K-half (cc>>1), 16-byte chunks 4*(cc&1)..+3, XOR-swizzled with (row & 7)
-        uint8_t* half = p_row + (cc >> 1) * kTileBytes;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 w;
-          w.x = pack_bf16x2(e[q4 * 8 + 0], e[q4 * 8 + 1]);
-          w.y = pack_bf16x2(e[q4 * 8 + 2], e[q4 * 8 + 3]);
-          w.z = pack_bf16x2(e[q4 * 8 + 4], e[q4 * 8 + 5]);
-          w.w = pack_bf16x2(e[q4 * 8 + 6], e[q4 * 8 + 7]);
-          const uint32_t chunk = static_cast<uint32_t>((cc & 1) * 4 + q4) ^ sw;
-          *reinterpret_cast<uint4*>(half + chunk * 16) = w;
-        }
+        tmem_st32(p_addr + hh * 32, pk);
       }
-      l = fmaf(l, alpha, rs);
-      m = mx;
-      alpha_prev = alpha;
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P visible to the tensor core
+      l = fmaf(l, alpha, (rs0 + rs1) + (rs2 + rs3));
+      tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_p_full(t));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p_full(t));
     }
-    if (ok && nblk > 0) {
-      ok = mbar_wait(bar_pv_full(t), (nblk - 1) & 1, cta_abort, a.status);
-      if (ok) {
-        tc_fence_after();
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          tmem_ld32(pv_addr + hh * 32, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[hh * 32 + i] = fmaf(o[hh * 32 + i], alpha_prev, __uint_as_float(r[i]));
-        }
-      }
-    }
+
+    // ---- epilogue: O / l ----
+    if (ok && nblk > 0) ok = mbar_wait(bar_pv_full(t), (nblk - 1) & 1, cta_abort, a.status);
     const int qrow = (qg * QT + t) * kTileM + row;
-    if (ok && nblk > 0 && qrow < a.n_q) {
+    if (ok && nblk > 0) {
+      tc_fence_after();
       const float inv = 1.f / l;
-      const size_t rowidx = (static_cast<size_t>(b) * a.n_q + qrow) * a.heads + h;
-      if (a.final_bf16) {
-        uint4* dst = reinterpret_cast<uint4*>(a.out + rowidx * kHeadDim);
+      const size_t rowidx = (static_cast<size_t>(b) * a.n_q + (qrow < a.n_q ? qrow : 0)) * a.heads + h;
+      const size_t prow = static_cast<size_t>(split) * a.batch * a.n_q * a.heads + rowidx;
 #pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          uint4 w;
-          w.x = pack_bf16x2(o[q4 * 8 + 0] * inv, o[q4 * 8 + 1] * inv);
-          w.y = pack_bf16x2(o[q4 * 8 + 2] * inv, o[q4 * 8 + 3] * inv);
-          w.z = pack_bf16x2(o[q4 * 8 + 4] * inv, o[q4 * 8 + 5] * inv);
-          w.w = pack_bf16x2(o[q4 * 8 + 6] * inv, o[q4 * 8 + 7] * inv);
-          dst[q4] = w;
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t ob[32];
+        tmem_ld32(o_addr + hh * 32, ob);      // warp-wide: every lane takes part, also rows past n_q
+        tmem_wait_ld();
+        if (qrow < a.n_q) {
+          if (a.final_bf16) {
+            uint4* dst = reinterpret_cast<uint4*>(a.out + rowidx * kHeadDim + hh * 32);
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(ob[q4 * 8 + 0]) * inv, __uint_as_float(ob[q4 * 8 + 1]) * inv);
+              w.y = pack_bf16x2(__uint_as_float(ob[q4 * 8 + 2]) * inv, __uint_as_float(ob[q4 * 8 + 3]) * inv);
+              w.z = pack_bf16x2(__uint_as_float(ob[q4 * 8 + 4]) * inv, __uint_as_float(ob[q4 * 8 + 5]) * inv);
+              w.w = pack_bf16x2(__uint_as_float(ob[q4 * 8 + 6]) * inv, __uint_as_float(ob[q4 * 8 + 7]) * inv);
+              dst[q4] = w;
+            }
+          } else {
+            float4* dst = reinterpret_cast<float4*>(a.part_o + prow * kHeadDim + hh * 32);
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4)
+              dst[q4] = make_float4(__uint_as_float(ob[q4 * 4 + 0]) * inv, __uint_as_float(ob[q4 * 4 + 1]) * inv,
+                                    __uint_as_float(ob[q4 * 4 + 2]) * inv, __uint_as_float(ob[q4 * 4 + 3]) * inv);
+          }
         }
-      } else {
-        const size_t prow = static_cast<size_t>(split) * a.batch * a.n_q * a.heads + rowidx;
-        float4* dst = reinterpret_cast<float4*>(a.part_o + prow * kHeadDim);
-#pragma unroll
-        for (int q4 = 0; q4 < 16; ++q4)
-          dst[q4] = make_float4(o[q4 * 4 + 0] * inv, o[q4 * 4 + 1] * inv, o[q4 * 4 + 2] * inv, o[q4 * 4 + 3] * inv);
-        a.part_lse[prow] = (m * c + log2f(l)) * 0.6931471805599453f;
       }
+      if (qrow < a.n_q && !a.final_bf16) a.part_lse[prow] = (m * c + log2f(l)) * 0.6931471805599453f;
     }
   }
 
@@ -451,7 +519,7 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == kMmaWarp) {
+  if (warp == kFirstMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -501,14 +569,14 @@ int launch_attention(const AttnLaunch& a, cudaStream_t stream) {
       GCT_CUDA_CHECK(cudaFuncSetAttribute(gct_attn_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       attr_set = true;
     }
-    gct_attn_kernel<2><<<static_cast<unsigned>(grid), 2 * 128 + 64, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
+    gct_attn_kernel<2><<<static_cast<unsigned>(grid), kThreads<2>, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
   } else {
     static bool attr_set = false;
     if (!attr_set) {
       GCT_CUDA_CHECK(cudaFuncSetAttribute(gct_attn_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       attr_set = true;
     }
-    gct_attn_kernel<1><<<static_cast<unsigned>(grid), 128 + 64, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
+    gct_attn_kernel<1><<<static_cast<unsigned>(grid), kThreads<1>, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
   }
   GCT_CUDA_CHECK(cudaGetLastError());
   return GCT_OK;
