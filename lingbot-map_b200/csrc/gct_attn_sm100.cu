@@ -430,43 +430,66 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       const float mc = m * c;
 
-      // P (and O) of this tile are free once the PV product of the previous block has completed
-      if (j > 0) {
-        if (!(ok = mbar_wait(bar_pv_full(t), (j - 1) & 1, cta_abort, a.status))) break;
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {   // rare: rescale this warp's 32 rows of O in TMEM
-          uint32_t ob[32];
+      // P (and O) of this tile are free once the PV product of the previous block has completed.  The wait
+      // sits in the middle of the exponential sweep, right before the first store of P, so that the
+      // round trip softmax -> MMA warp -> tensor core -> mbarrier hides under the first half of the sweep.
+      auto wait_prev_pv_and_rescale = [&]() -> bool {
+        if (j > 0) {
+          if (!mbar_wait(bar_pv_full(t), (j - 1) & 1, cta_abort, a.status)) return false;
+          tc_fence_after();
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {   // rare: rescale this warp's 32 rows of O in TMEM
+            uint32_t ob[32];
 #pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            tmem_ld32(o_addr + hh * 32, ob);
-            tmem_wait_ld();
+            for (int hh = 0; hh < 2; ++hh) {
+              tmem_ld32(o_addr + hh * 32, ob);
+              tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) ob[i] = __float_as_uint(__uint_as_float(ob[i]) * alpha);
-            tmem_st32(o_addr + hh * 32, ob);
+              for (int i = 0; i < 32; ++i) ob[i] = __float_as_uint(__uint_as_float(ob[i]) * alpha);
+              tmem_st32(o_addr + hh * 32, ob);
+            }
+          }
+        }
+        return true;
+      };
+      // P = exp2(S*c - m*c), software-pipelined over pairs of logits so that the exponentials (the scarce
+      // pipe) are interleaved with independent work: pair p+4 gets its packed FFMA, pair p its two EX2,
+      // pair p-2 its packed add into the row sum and its bf16 conversion (two K values per TMEM column).
+      const float2 c2 = make_float2(c, c), nmc2 = make_float2(-mc, -mc);
+      float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+      uint32_t pk[32];
+      auto pair_ffma = [&](int q) {
+        const float2 x = __ffma2_rn(make_float2(__uint_as_float(s[2 * q]), __uint_as_float(s[2 * q + 1])), c2, nmc2);
+        s[2 * q] = __float_as_uint(x.x);
+        s[2 * q + 1] = __float_as_uint(x.y);
+      };
+      auto pair_exp = [&](int q) {
+        s[2 * q] = __float_as_uint(fast_exp2(__uint_as_float(s[2 * q])));
+        s[2 * q + 1] = __float_as_uint(fast_exp2(__uint_as_float(s[2 * q + 1])));
+      };
+      auto pair_sum = [&](int q) {
+        const float2 e = make_float2(__uint_as_float(s[2 * q]), __uint_as_float(s[2 * q + 1]));
+        if (q & 1) acc1 = __fadd2_rn(acc1, e); else acc0 = __fadd2_rn(acc0, e);
+        pk[q & 31] = pack_bf16x2(e.x, e.y);
+      };
+#pragma unroll
+      for (int q = 0; q < 4; ++q) pair_ffma(q);
+#pragma unroll
+      for (int q = 0; q < 64; ++q) {
+        if (q + 4 < 64) pair_ffma(q + 4);
+        pair_exp(q);
+        if (q >= 2) {
+          pair_sum(q - 2);
+          if (q - 2 == 31) {                            // first 64 keys done
+            ok = wait_prev_pv_and_rescale();
+            if (ok) tmem_st32(p_addr, pk);
           }
         }
       }
-
-      // P = exp2(S*c - m*c), row sum, bf16 pairs (two K values per 32-bit TMEM column)
-      float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        uint32_t pk[32];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float e0 = fast_exp2(fmaf(__uint_as_float(s[hh * 64 + 2 * i + 0]), c, -mc));
-          const float e1 = fast_exp2(fmaf(__uint_as_float(s[hh * 64 + 2 * i + 1]), c, -mc));
-          const float e2 = fast_exp2(fmaf(__uint_as_float(s[hh * 64 + 2 * i + 2]), c, -mc));
-          const float e3 = fast_exp2(fmaf(__uint_as_float(s[hh * 64 + 2 * i + 3]), c, -mc));
-          rs0 += e0;
-          rs1 += e1;
-          rs2 += e2;
-          rs3 += e3;
-          pk[i] = pack_bf16x2(e0, e1);
-          pk[i + 1] = pack_bf16x2(e2, e3);
-        }
-        tmem_st32(p_addr + hh * 32, pk);
-      }
+      pair_sum(62);
+      pair_sum(63);
+      if (!ok) break;
+      tmem_st32(p_addr + 32, pk);
+      const float rs0 = acc0.x, rs1 = acc0.y, rs2 = acc1.x, rs3 = acc1.y;
       l = fmaf(l, alpha, (rs0 + rs1) + (rs2 + rs3));
       tmem_wait_st();
       tc_fence_before();
