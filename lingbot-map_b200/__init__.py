@@ -7,5 +7,7 @@ Everything computes on the GPU through the C ABI in libgct_b200.so; there is no 
 from . import _lib  # noqa: F401
 from .cache import B200KVCacheManager  # noqa: F401
 from . import ops  # noqa: F401
+from .block import B200Attention, B200Block, B200FrameAttention  # noqa: F401
+from . import select  # noqa: F401
 
-__all__ = ["B200KVCacheManager", "ops"]
+__all__ = ["B200KVCacheManager", "B200Attention", "B200Block", "B200FrameAttention", "ops", "select"]

@@ -1,0 +1,68 @@
+"""Drop-in structure of the host-side mirror, no GPU: parameter names equal the reference's, constructor
+signatures accept what the aggregator passes, and (where the reference checkout is importable) the rebinding
+makes the reference's own AggregatorStream build B200 blocks with an unchanged state_dict."""
+import inspect
+import json
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import lingbot_map_b200 as P
+
+G = os.path.join(os.path.dirname(__file__), "golden")
+REF = "/root/reference"
+
+
+def test_block_parameter_names_match_reference():
+    z = np.load(os.path.join(G, "block_stream_fp32.npz"))
+    ref_names = json.loads(bytes(z["param_names_json"]).decode())
+    blk = P.B200Block(dim=128, num_heads=2, init_values=0.01, qk_norm=True, rope=object(),
+                      kv_cache_sliding_window=3, kv_cache_scale_frames=2)
+    assert [n for n, _ in blk.named_parameters()] == ref_names
+    for name in ("attn_pre", "ffn_residual"):
+        assert callable(getattr(blk, name))
+    assert isinstance(blk.attn.proj, torch.nn.Linear)
+
+
+def test_manager_signature_accepts_aggregator_call():
+    """Keyword arguments of the call at lingbot_map/aggregator/stream.py:215-229."""
+    sig = inspect.signature(P.B200KVCacheManager.__init__)
+    for kw in ("num_blocks", "max_num_frames", "tokens_per_frame", "num_heads", "head_dim", "dtype", "device",
+               "num_special_tokens", "scale_frames", "sliding_window", "max_total_frames", "force_fp32", "fa3"):
+        assert kw in sig.parameters
+    fwd = inspect.signature(P.B200Block.forward)
+    for kw in ("x", "pos", "num_patches", "num_special", "num_frames", "enable_3d_rope", "kv_cache", "global_idx",
+               "num_frame_per_block", "num_frame_for_scale", "num_register_tokens"):
+        assert kw in fwd.parameters      # stream.py:508-520
+
+
+def test_head_dim_other_than_64_is_rejected():
+    with pytest.raises(ValueError):
+        P.B200Block(dim=96, num_heads=2)
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lingbot_map")), reason="reference checkout not present")
+def test_rebinding_builds_b200_blocks_in_reference_aggregator():
+    sys.path.insert(0, REF)
+    import lingbot_map.aggregator.stream as stream_mod
+    import lingbot_map.layers.flashinfer_cache as cache_mod
+    saved = (stream_mod.FlashInferBlock, cache_mod.FlashInferKVCacheManager, stream_mod.AggregatorStream.__init__)
+    kw = dict(img_size=56, patch_size=14, embed_dim=1024, depth=1, num_heads=16, patch_embed="conv",
+              enable_3d_rope=True, max_frame_num=32, kv_cache_sliding_window=3, kv_cache_scale_frames=2)
+    try:
+        torch.manual_seed(0)
+        ref = stream_mod.AggregatorStream(**kw)
+        P.select.install()
+        torch.manual_seed(0)
+        agg = stream_mod.AggregatorStream(**kw)
+        assert all(isinstance(b, P.B200Block) for b in agg.global_blocks)
+        assert all(isinstance(b.attn, P.B200FrameAttention) for b in agg.frame_blocks)
+        assert list(agg.state_dict().keys()) == list(ref.state_dict().keys())
+        agg.load_state_dict(ref.state_dict(), strict=True)
+        assert cache_mod.FlashInferKVCacheManager is P.B200KVCacheManager
+    finally:
+        stream_mod.FlashInferBlock, cache_mod.FlashInferKVCacheManager, stream_mod.AggregatorStream.__init__ = saved
+        stream_mod.AggregatorStream._b200_wrapped = False
