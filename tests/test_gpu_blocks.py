@@ -1,0 +1,131 @@
+"""Block-level parity on the GPU: B200Block / B200FrameAttention against outputs recorded from the reference's
+FlashInferBlock (paged fp32 path), SDPABlock and Attention on CPU (tests/golden/*.npz).
+
+Weights are fp32 and the Linear layers run in fp32; q/k/v are rounded to bf16 by the CUDA prologue, attention runs
+on bf16 tensor cores.  Tolerance on block outputs: 2e-2 max-abs and cosine >= 0.9999 (float64)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import seeded
+import lingbot_map_b200 as P
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(__file__), "golden")
+DEV = "cuda:0"
+
+
+class Rope2dStub:
+    """Carries the base frequency the way RotaryPositionEmbedding2D does (rope.py:81-86)."""
+    base_frequency = 100.0
+
+
+def close(got, want, tag, max_abs=2e-2, cos=0.9999):
+    g = got.double().cpu().numpy().ravel()
+    w = np.asarray(want, np.float64).ravel()
+    c = float(g @ w / (np.linalg.norm(g) * np.linalg.norm(w)))
+    d = float(np.abs(g - w).max())
+    assert np.isfinite(g).all() and d <= max_abs and c >= cos, f"{tag}: max_abs={d:.3e} cosine={c:.7f}"
+
+
+def rope3d_pos(f_start, n_frames, pph, ppw, ns):
+    """Complex frequency tensor [1,1,N,32] as WanRotaryPosEmbed.forward returns it (rope.py:336-425)."""
+    from oracle import gct_oracle as O
+    ang = np.concatenate([O.rope3d_angles(f, pph, ppw, ns) for f in range(f_start, f_start + n_frames)], axis=0)
+    z = torch.polar(torch.ones(ang.shape, dtype=torch.float64), torch.from_numpy(ang))
+    return z[None, None].to(DEV)
+
+
+@pytest.mark.parametrize("kf", [2, 1])
+def test_block_stream_matches_reference(kf):
+    z = np.load(os.path.join(G, "block_stream_fp32.npz"))
+    dim, H, pph, ppw, ns, scale, window = 128, 2, 3, 4, 6, 2, 3
+    Ptok = ns + pph * ppw
+    blk = P.B200Block(dim=dim, num_heads=H, init_values=0.01, qk_norm=True, rope=Rope2dStub(),
+                      kv_cache_sliding_window=window, kv_cache_scale_frames=scale).eval().to(DEV)
+    seeded.fill_module_(blk, 21)
+    mgr = P.B200KVCacheManager(num_blocks=1, max_num_frames=scale + window + 16, tokens_per_frame=Ptok, num_heads=H,
+                               head_dim=64, dtype=torch.float32, device=DEV, scale_frames=scale,
+                               sliding_window=window, max_total_frames=40)
+    tag = f"paged_kf{kf}"
+    kw = dict(num_patches=Ptok - ns, num_special=ns, enable_3d_rope=True, kv_cache=mgr, global_idx=0,
+              num_frame_for_scale=scale, num_register_tokens=4)
+    tfp = 0
+    with torch.no_grad():
+        x = torch.from_numpy(seeded.randn(500, 1, scale * Ptok, dim)).to(DEV)
+        y = blk(x, pos=rope3d_pos(0, scale, pph, ppw, ns), num_frames=scale, num_frame_per_block=scale, **kw)
+        close(y, z[f"{tag}_phase1"], "phase 1")
+        tfp += scale
+        for i in range(scale, scale + 8):
+            is_kf = kf <= 1 or (i - scale) % kf == 0
+            mgr._skip_append = not is_kf
+            x = torch.from_numpy(seeded.randn(500 + i, 1, Ptok, dim)).to(DEV)
+            y = blk(x, pos=rope3d_pos(tfp, 1, pph, ppw, ns), num_frames=1, num_frame_per_block=1, **kw)
+            close(y, z[f"{tag}_frame{i}"], f"frame {i} ({'KF' if is_kf else 'non-KF'})")
+            if is_kf:
+                tfp += 1
+    mgr._skip_append = False
+    # page table and eviction decisions bit-exact with the reference run
+    assert mgr.build_visible_page_table(0) == list(z[f"{tag}_visible_end"])
+    assert mgr.compute_last_page_len(0) == int(z[f"{tag}_last_len_end"][0])
+    assert mgr.device_status() == 0
+
+
+def test_block_attn_pre_contract():
+    """attn_pre returns (q, k, v) [tokens, H, 64] like block.py:217-227 and equals what the fused append writes."""
+    dim, H, pph, ppw, ns = 128, 2, 3, 4, 6
+    Ptok = ns + pph * ppw
+    blk = P.B200Block(dim=dim, num_heads=H, init_values=0.01, qk_norm=True, rope=Rope2dStub()).eval().to(DEV)
+    seeded.fill_module_(blk, 5)
+    mgr = P.B200KVCacheManager(1, 21, Ptok, H, 64, device=DEV, scale_frames=2, sliding_window=3, max_total_frames=40)
+    x = torch.from_numpy(seeded.randn(1, 1, Ptok, dim)).to(DEV)
+    pos = rope3d_pos(3, 1, pph, ppw, ns)
+    with torch.no_grad():
+        q, k, v = blk.attn_pre(x, pos=pos, enable_3d_rope=True)
+        blk(x, pos=pos, num_frames=1, enable_3d_rope=True, kv_cache=mgr, global_idx=0)
+    assert q.shape == (Ptok, H, 64) and q.dtype == torch.bfloat16
+    kk, vv = mgr._gather_kv(0)
+    # cache order: patch page first, then the special page (flashinfer_cache.py:446-450)
+    assert torch.equal(kk, torch.cat([k[ns:], k[:ns]])) and torch.equal(vv, torch.cat([v[ns:], v[:ns]]))
+
+
+def test_frame_attention_matches_reference():
+    z = np.load(os.path.join(G, "prepare_qkv_fp32.npz"))
+    dim, H, pph, ppw, ns = 128, 2, 3, 4, 6
+    N = ns + pph * ppw
+    fa = P.B200FrameAttention(dim, num_heads=H, qk_norm=True, rope=Rope2dStub()).eval().to(DEV)
+    seeded.fill_module_(fa, 11)
+    x = torch.from_numpy(seeded.randn(123, 2, N, dim)).to(DEV)
+    pos = torch.from_numpy(z["rope2d_pos"]).to(DEV)[None].expand(2, -1, -1)
+    with torch.no_grad():
+        y = fa(x, pos=pos)
+    close(y, z["frame_attn_out"], "frame attention")
+
+
+def test_bf16_autocast_path():
+    """demo.py casts the aggregator to bf16 and runs under autocast (demo.py:458-460,545): bf16 weights and
+    activations, bf16 LayerNorm parameters."""
+    dim, H, pph, ppw, ns = 128, 2, 3, 4, 6
+    Ptok = ns + pph * ppw
+    blk = P.B200Block(dim=dim, num_heads=H, init_values=0.01, qk_norm=True, rope=Rope2dStub(),
+                      kv_cache_sliding_window=3, kv_cache_scale_frames=2).eval().to(DEV)
+    seeded.fill_module_(blk, 21)
+    ref = P.B200Block(dim=dim, num_heads=H, init_values=0.01, qk_norm=True, rope=Rope2dStub(),
+                      kv_cache_sliding_window=3, kv_cache_scale_frames=2).eval().to(DEV)
+    seeded.fill_module_(ref, 21)
+    blk = blk.to(torch.bfloat16)
+    mk = lambda: P.B200KVCacheManager(1, 21, Ptok, H, 64, device=DEV, scale_frames=2, sliding_window=3,
+                                      max_total_frames=40)
+    m1, m2 = mk(), mk()
+    for i in range(5):
+        x = torch.from_numpy(seeded.randn(900 + i, 1, Ptok, dim)).to(DEV)
+        pos = rope3d_pos(i, 1, pph, ppw, ns)
+        with torch.no_grad():
+            want = ref(x, pos=pos, num_frames=1, enable_3d_rope=True, kv_cache=m2, global_idx=0)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                got = blk(x.to(torch.bfloat16), pos=pos, num_frames=1, enable_3d_rope=True, kv_cache=m1, global_idx=0)
+        assert got.dtype == torch.bfloat16
+        close(got, want.double().cpu().numpy(), f"bf16 frame {i}", max_abs=8e-2, cos=0.999)
+    assert m1.build_visible_page_table(0) == m2.build_visible_page_table(0)
