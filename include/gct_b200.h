@@ -178,6 +178,12 @@ int gct_rope2d_table(int pph, int ppw, int num_special, float base, float* cs_ou
  * out_dev [n_q, H, 64] bf16; lse_out_dev optional. */
 int gct_lse_merge(const float* parts_dev, const float* lse_dev, int groups, int n_q, int heads, void* out_dev,
                   float* lse_out_dev, void* stream);
+/* Same with explicit distances (in floats) between consecutive groups, for partials that arrive packed as
+ * one [O | lse] record per rank from a single all-gather (no counterpart in the reference, which is
+ * single-GPU). */
+int gct_lse_merge_strided(const float* parts_dev, const float* lse_dev, int groups, int n_q, int heads,
+                          int64_t parts_group_stride, int64_t lse_group_stride, void* out_dev, float* lse_out_dev,
+                          void* stream);
 
 /* Paged attention that allocates nothing (this entry point has no counterpart in the reference).
  * For hosts that cannot call cudaMalloc - e.g. a process that gave all device memory to its own pool

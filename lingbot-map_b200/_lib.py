@@ -67,6 +67,7 @@ SIGNATURES = {
     "gct_rope3d_table": (_i, [_i, _i, _i, _i, _vp, _vp]),
     "gct_rope2d_table": (_i, [_i, _i, _i, C.c_float, _vp, _vp]),
     "gct_lse_merge": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
+    "gct_lse_merge_strided": (_i, [_vp, _vp, _i, _i, _i, _i64, _i64, _vp, _vp, _vp]),
     "gct_attn_paged_static": (_i, [_vp, _i, _i, _i, _pi32, _i, _i, _vp, _i, _vp, _vp, _pi]),
 }
 

@@ -280,13 +280,18 @@ class B200KVCacheManager:
                                                 _stream_ptr(self.device)))
         return (out, lse) if return_lse else out
 
-    def compute_attention_partial(self, block_idx: int, q: Tensor):
+    def compute_attention_partial(self, block_idx: int, q: Tensor, out: Optional[Tensor] = None,
+                                  lse: Optional[Tensor] = None):
         """Attention over the planned page range only: (out fp32 [q_len,H,D], lse fp32 [q_len,H]) for a
-        later log-sum-exp merge across KV shards."""
+        later log-sum-exp merge across KV shards.  `out` / `lse` may be views of a caller's send buffer."""
         self._require_device()
         q = self._check_frame_tensor(q, "q")
-        out = torch.empty(q.shape, dtype=torch.float32, device=self.device)
-        lse = torch.empty(q.shape[0], self.num_heads, dtype=torch.float32, device=self.device)
+        if out is None:
+            out = torch.empty(q.shape, dtype=torch.float32, device=self.device)
+        if lse is None:
+            lse = torch.empty(q.shape[0], self.num_heads, dtype=torch.float32, device=self.device)
+        if not (out.is_contiguous() and lse.is_contiguous() and out.dtype == lse.dtype == torch.float32):
+            raise ValueError("out and lse must be contiguous float32 tensors")
         self._check(self._lib.gct_mgr_attention_partial(self._handle, block_idx, q.data_ptr(), _dtype_code(q),
                                                         q.shape[0], out.data_ptr(), lse.data_ptr(),
                                                         _stream_ptr(self.device)))

@@ -90,8 +90,9 @@ struct PrepLaunch {
 int launch_prep(const PrepLaunch& p, cudaStream_t stream);
 
 int launch_cast_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream_t stream);
+// parts_stride / lse_stride: elements between consecutive groups (0 = densely packed).
 int launch_merge(const float* parts, const float* lse, int groups, int64_t rows /* n_q*H */, __nv_bfloat16* out_bf16,
-                 float* out_f32, float* lse_out, cudaStream_t stream);
+                 float* out_f32, float* lse_out, cudaStream_t stream, int64_t parts_stride = 0, int64_t lse_stride = 0);
 int launch_rope3d_table(int f, int pph, int ppw, int ns, float* cs, cudaStream_t stream);
 int launch_rope2d_table(int pph, int ppw, int ns, float base, float* cs, cudaStream_t stream);
 

@@ -142,17 +142,18 @@ __global__ void gct_cast_kernel(const float* __restrict__ src, __nv_bfloat16* __
 //   out = sum_g w_g O_g / sum_g w_g,  w_g = exp(lse_g - max_g lse_g)
 __global__ void __launch_bounds__(256)
 gct_merge_kernel(const float* __restrict__ parts, const float* __restrict__ lse, int groups, int64_t rows,
-                 __nv_bfloat16* __restrict__ out_bf16, float* __restrict__ out_f32, float* __restrict__ lse_out) {
+                 int64_t parts_stride, int64_t lse_stride, __nv_bfloat16* __restrict__ out_bf16,
+                 float* __restrict__ out_f32, float* __restrict__ lse_out) {
   const int lane = threadIdx.x & 31;
   const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (row >= rows) return;
   float mx = -INFINITY;
-  for (int g = 0; g < groups; ++g) mx = fmaxf(mx, lse[static_cast<int64_t>(g) * rows + row]);
+  for (int g = 0; g < groups; ++g) mx = fmaxf(mx, lse[static_cast<int64_t>(g) * lse_stride + row]);
   float den = 0.f;
   float2 acc = make_float2(0.f, 0.f);
   for (int g = 0; g < groups; ++g) {
-    const float w = __expf(lse[static_cast<int64_t>(g) * rows + row] - mx);
-    const float2 v = *reinterpret_cast<const float2*>(parts + (static_cast<int64_t>(g) * rows + row) * kHeadDim + 2 * lane);
+    const float w = __expf(lse[static_cast<int64_t>(g) * lse_stride + row] - mx);
+    const float2 v = *reinterpret_cast<const float2*>(parts + static_cast<int64_t>(g) * parts_stride + row * kHeadDim + 2 * lane);
     acc.x = fmaf(w, v.x, acc.x);
     acc.y = fmaf(w, v.y, acc.y);
     den += w;
@@ -239,10 +240,14 @@ int launch_cast_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream
 }
 
 int launch_merge(const float* parts, const float* lse, int groups, int64_t rows, __nv_bfloat16* out_bf16,
-                 float* out_f32, float* lse_out, cudaStream_t stream) {
+                 float* out_f32, float* lse_out, cudaStream_t stream, int64_t parts_stride, int64_t lse_stride) {
   if (groups <= 0 || rows <= 0) return fail(GCT_ERR_INVALID, "merge: bad shape");
+  if (parts_stride <= 0) parts_stride = rows * kHeadDim;
+  if (lse_stride <= 0) lse_stride = rows;
+  if (parts_stride % 2 != 0) return fail(GCT_ERR_INVALID, "merge: group stride of the partial outputs must be even");
   const int blocks = static_cast<int>((rows * 32 + 255) / 256);
-  gct_merge_kernel<<<blocks, 256, 0, stream>>>(parts, lse, groups, rows, out_bf16, out_f32, lse_out);
+  gct_merge_kernel<<<blocks, 256, 0, stream>>>(parts, lse, groups, rows, parts_stride, lse_stride, out_bf16, out_f32,
+                                               lse_out);
   GCT_CUDA_CHECK(cudaGetLastError());
   return GCT_OK;
 }

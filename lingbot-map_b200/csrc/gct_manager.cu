@@ -743,4 +743,14 @@ int gct_lse_merge(const float* parts_dev, const float* lse_dev, int groups, int 
                       nullptr, lse_out_dev, static_cast<cudaStream_t>(stream));
 }
 
+int gct_lse_merge_strided(const float* parts_dev, const float* lse_dev, int groups, int n_q, int heads,
+                          int64_t parts_group_stride, int64_t lse_group_stride, void* out_dev, float* lse_out_dev,
+                          void* stream) {
+  if (parts_dev == nullptr || lse_dev == nullptr || out_dev == nullptr)
+    return fail(GCT_ERR_INVALID, "gct_lse_merge_strided: null argument");
+  if (parts_group_stride <= 0 || lse_group_stride <= 0) return fail(GCT_ERR_INVALID, "gct_lse_merge_strided: bad stride");
+  return launch_merge(parts_dev, lse_dev, groups, static_cast<int64_t>(n_q) * heads, static_cast<__nv_bfloat16*>(out_dev),
+                      nullptr, lse_out_dev, static_cast<cudaStream_t>(stream), parts_group_stride, lse_group_stride);
+}
+
 }  // extern "C"

@@ -275,3 +275,44 @@ def test_full_geometry_properties():
     assert float((merged.float() - full.float()).abs().max()) < 1e-2
     assert cosine64(merged.float().cpu().numpy(), full.float().cpu().numpy()) > 0.99999
     assert m.device_status() == 0
+
+
+def test_sharded_records_and_strided_merge():
+    """The multi-GPU record format on one GPU: two page shards computed one after the other into packed
+    [O | lse] records (what each rank all-gathers), merged by gct_lse_merge_strided; plus the world-size-1
+    path of sharded_attention and the empty-shard record."""
+    from lingbot_map_b200 import distributed as D
+    tpf, H = 200, 2
+    m = P.B200KVCacheManager(2, 21, tpf, H, 64, device=DEV, scale_frames=2, sliding_window=3, max_total_frames=60)
+    orc = O.PagedCacheOracle(2, tpf, H, 64, scale_frames=2, sliding_window=3, max_total_frames=60)
+    for t in range(9):
+        for b in range(2):
+            k, v = seeded.randn(20 * t + b, tpf, H, 64), seeded.randn(700 + 20 * t + b, tpf, H, 64)
+            m.append_frame(b, bf(k), bf(v))
+            m.evict_frames(b, 2, 3)
+            orc.append_frame(b, r(k), r(v))
+            orc.evict_frames(b, 2, 3)
+    q = seeded.randn(4242, tpf, H, 64)
+    kk, vv = orc.gather_kv(1)
+    want = O.attention(r(q), kk, vv)[0]
+    n_pages = len(m.build_visible_page_table(0))
+    n = tpf * H * 64
+    world = 3
+    rec = torch.empty(world, D.record_floats(tpf, H), dtype=torch.float32, device=DEV)
+    for rank in range(2):
+        lo, hi = D.shard_page_range(n_pages, rank, 2)
+        m.plan(lo, hi)
+        m.compute_attention_partial(1, bf(q), out=rec[rank, :n].view(tpf, H, 64), lse=rec[rank, n:].view(tpf, H))
+    D.pack_empty_record(rec[2], tpf, H)                       # a rank that owns no page
+    out = torch.empty(tpf, H, 64, dtype=torch.bfloat16, device=DEV)
+    _lib.check(_lib.load().gct_lse_merge_strided(rec.data_ptr(), rec.data_ptr() + 4 * n, world, tpf, H, rec.shape[1],
+                                                 rec.shape[1], out.data_ptr(), None,
+                                                 torch.cuda.current_stream().cuda_stream))
+    assert_close(out, want, "strided merge of 2 shards + empty record")
+    assert_close(D.merge_records_reference(rec, tpf, H).float(), want, "torch merge")
+    # world size 1 through the public helper (plans at block 0, reuses the plan at block 1)
+    m._shard_plan = None
+    o0 = D.sharded_attention(m, 0, bf(q), 0, 1)
+    o1 = D.sharded_attention(m, 1, bf(q), 0, 1)
+    assert_close(o1, want, "sharded_attention world=1")
+    assert o0.shape == o1.shape and m.device_status() == 0
