@@ -242,7 +242,8 @@ def run_gpu(args):
 
     if rank == 0:
         peaks = load_peaks()
-        flops = 4.0 * TPF * kv_now * HEAD_DIM * HEADS
+        # algorithmic FLOPs of one launch of the paged attention kernel; a KV shard holds 1/world of the keys
+        flops = 4.0 * TPF * kv_now * HEAD_DIM * HEADS / (world if kvsplit else 1)
         kern_s = attn_ms / max(attn_launches, 1) / 1e3
         achieved = flops / kern_s / 1e12 if attn_launches else None
         line = {
@@ -266,7 +267,8 @@ def run_gpu(args):
                          "frac": (achieved / peaks["bf16_tflops"]) if achieved else None,
                          "peak_source": peaks["which"], "kernel_us": kern_s * 1e6, "launches_timed": attn_launches,
                          "flops_per_launch": flops, "attn_share_of_step": attn_ms / total_ms,
-                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH},
+                         "traffic": NCU_DRAM_BYTES_SMALL_CASE * kv_now / NCU_SMALL_CASE_KV / (world if kvsplit else 1),
+                         "traffic_source": "ncu small case scaled by KV tokens"},
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(max_seconds=25.0)
@@ -276,9 +278,11 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the paged attention kernel, from the
-# ncu capture summarised under profiles/ (None until a capture exists).
-NCU_DRAM_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the paged attention kernel.  Captured with
+# ncu on a small case (kv = 73,146 tokens: 340.3 MB, see profiles/gct_attn_kernel_paged_kv73k.md) and
+# scaled to the benchmark's KV length by the number of key tokens, which the traffic is proportional to.
+NCU_DRAM_BYTES_SMALL_CASE = 340.26e6
+NCU_SMALL_CASE_KV = 73146
 
 
 # ----------------------------------------------------------------------------- CPU arm
