@@ -7,21 +7,9 @@
 namespace gct {
 namespace {
 
-__device__ __forceinline__ float2 load2(const void* base, int dtype, size_t elem) {
-  if (dtype == GCT_F32) {
-    return *reinterpret_cast<const float2*>(static_cast<const float*>(base) + elem);
-  }
-  const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(static_cast<const __nv_bfloat16*>(base) + elem);
-  return __bfloat1622float2(v);
-}
-
-__device__ __forceinline__ float warp_sum(float x) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
-  return x;
-}
-
-// One warp per (token, group of heads); lane m owns elements (2m, 2m+1) of each 64-wide row.
+// One warp per (token, group of four heads): lanes 8h..8h+7 own head h of the group, lane part s = lane & 7
+// owns the eight consecutive elements 8s..8s+7 of the 64-wide row (one 16-byte bf16 or two 16-byte fp32
+// loads), so a warp moves 512 contiguous bytes per tensor and all of q, k, v are in flight at once.
 //   LayerNorm(64), eps 1e-5, affine            lingbot_map/layers/attention.py:58-59,415
 //   3-D RoPE: pair (2m,2m+1) rotated by angle m lingbot_map/layers/rope.py:450-461
 //   2-D RoPE: inside each 32-wide half pair (j, j+16) rotated by angle j; table entry 16*half + j
@@ -29,56 +17,122 @@ __device__ __forceinline__ float warp_sum(float x) {
 //   page write of K/V rows                     lingbot_map/layers/flashinfer_cache.py:503-505,547-549
 constexpr int kHeadsPerWarp = 4;
 
-__device__ __forceinline__ float2 norm_rope(float2 x, const float* w, const float* bia, float2 cs_mine,
-                                            float2 cs_2d, int rope_mode, int lane) {
+struct Row8 {
+  float v[8];
+};
+
+__device__ __forceinline__ Row8 load8(const void* base, int dtype, size_t elem) {
+  Row8 r;
+  if (dtype == GCT_F32) {
+    const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(base) + elem);
+    const float4 b = *reinterpret_cast<const float4*>(static_cast<const float*>(base) + elem + 4);
+    r.v[0] = a.x; r.v[1] = a.y; r.v[2] = a.z; r.v[3] = a.w;
+    r.v[4] = b.x; r.v[5] = b.y; r.v[6] = b.z; r.v[7] = b.w;
+  } else {
+    const uint4 u = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(base) + elem);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+      r.v[2 * i] = f.x;
+      r.v[2 * i + 1] = f.y;
+    }
+  }
+  return r;
+}
+
+__device__ __forceinline__ void store8(__nv_bfloat16* dst, const Row8& r) {
+  uint4 u;
+  __nv_bfloat162 p0 = __floats2bfloat162_rn(r.v[0], r.v[1]), p1 = __floats2bfloat162_rn(r.v[2], r.v[3]);
+  __nv_bfloat162 p2 = __floats2bfloat162_rn(r.v[4], r.v[5]), p3 = __floats2bfloat162_rn(r.v[6], r.v[7]);
+  u.x = *reinterpret_cast<uint32_t*>(&p0);
+  u.y = *reinterpret_cast<uint32_t*>(&p1);
+  u.z = *reinterpret_cast<uint32_t*>(&p2);
+  u.w = *reinterpret_cast<uint32_t*>(&p3);
+  *reinterpret_cast<uint4*>(dst) = u;
+}
+
+// sum over the eight lanes of a row
+__device__ __forceinline__ float row_sum(float x) {
+  x += __shfl_xor_sync(0xffffffffu, x, 1);
+  x += __shfl_xor_sync(0xffffffffu, x, 2);
+  x += __shfl_xor_sync(0xffffffffu, x, 4);
+  return x;
+}
+
+// cs: the eight (cos, sin) pairs this lane needs.  3-D: entries 4s..4s+3 (pairs of its 8 elements), only
+// cs[0..3] used.  2-D: entries 16*half + 8*(s&1) + i for its elements i = 0..7.
+__device__ __forceinline__ void norm_rope8(Row8& x, const float* w, const float* bia, const float2 (&cs)[8],
+                                           int rope_mode, int part) {
   if (w != nullptr) {
-    const float mean = warp_sum(x.x + x.y) * (1.f / 64.f);
-    const float dx = x.x - mean, dy = x.y - mean;
-    const float var = warp_sum(dx * dx + dy * dy) * (1.f / 64.f);
-    const float rstd = rsqrtf(var + 1e-5f);
-    const float2 ww = *reinterpret_cast<const float2*>(w + 2 * lane);
-    const float2 bb = *reinterpret_cast<const float2*>(bia + 2 * lane);
-    x.x = dx * rstd * ww.x + bb.x;
-    x.y = dy * rstd * ww.y + bb.y;
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sum += x.v[i];
+    const float mean = row_sum(sum) * (1.f / 64.f);
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      x.v[i] -= mean;
+      sq += x.v[i] * x.v[i];
+    }
+    const float rstd = rsqrtf(row_sum(sq) * (1.f / 64.f) + 1e-5f);
+    const float4 w0 = *reinterpret_cast<const float4*>(w + 8 * part), w1 = *reinterpret_cast<const float4*>(w + 8 * part + 4);
+    const float4 b0 = *reinterpret_cast<const float4*>(bia + 8 * part), b1 = *reinterpret_cast<const float4*>(bia + 8 * part + 4);
+    const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x.v[i] = x.v[i] * rstd * ww[i] + bb[i];
   }
   if (rope_mode == GCT_ROPE_3D) {
-    const float c = cs_mine.x, s = cs_mine.y;
-    const float a = x.x * c - x.y * s;
-    const float b = x.x * s + x.y * c;
-    x.x = a;
-    x.y = b;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float a = x.v[2 * i] * cs[i].x - x.v[2 * i + 1] * cs[i].y;
+      const float b = x.v[2 * i] * cs[i].y + x.v[2 * i + 1] * cs[i].x;
+      x.v[2 * i] = a;
+      x.v[2 * i + 1] = b;
+    }
   } else if (rope_mode == GCT_ROPE_2D) {
-    // lane m holds elements e = 2m, 2m+1; inside the half (e % 32) the partner of e is e +/- 16,
-    // i.e. lane m ^ 8.  First 16 of a half: out = x*cos - partner*sin; last 16: out = x*cos + partner*sin.
-    const float px = __shfl_xor_sync(0xffffffffu, x.x, 8);
-    const float py = __shfl_xor_sync(0xffffffffu, x.y, 8);
-    const bool upper = (lane & 8) != 0;
-    // angle index for element e: 16*half + (e % 16); elements 2m and 2m+1 use consecutive angles
-    const float sgn = upper ? 1.f : -1.f;
-    x.x = x.x * cs_mine.x + sgn * px * cs_mine.y;
-    x.y = x.y * cs_2d.x + sgn * py * cs_2d.y;
+    // element e' = 8*(part & 3) + i inside its 32-wide half; its partner e' +/- 16 lives two lanes away.
+    // First 16 of a half: out = x*cos - partner*sin; last 16: out = x*cos + partner*sin.
+    const float sgn = (part & 2) ? 1.f : -1.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float partner = __shfl_xor_sync(0xffffffffu, x.v[i], 2);
+      x.v[i] = x.v[i] * cs[i].x + sgn * partner * cs[i].y;
+    }
   }
-  return x;
 }
 
 __global__ void __launch_bounds__(256) gct_prep_kernel(const PrepLaunch p) {
   const int lane = threadIdx.x & 31;
+  const int part = lane & 7;
   const int wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int head_groups = (p.heads + kHeadsPerWarp - 1) / kHeadsPerWarp;
   const int token = wid / head_groups;
   if (token >= p.tokens) return;
-  const int h0 = (wid - token * head_groups) * kHeadsPerWarp;
+  const int h = (wid - token * head_groups) * kHeadsPerWarp + (lane >> 3);
+  const bool active = h < p.heads;          // inactive lanes still take part in the shuffles
+  const int hh = active ? h : p.heads - 1;
   const int tf = token % p.tokens_per_frame;
 
   // rotation coefficients of this lane
-  float2 cs_mine = make_float2(1.f, 0.f), cs_2d = make_float2(1.f, 0.f);
+  float2 cs[8];
   if (p.rope_mode == GCT_ROPE_3D) {
-    cs_mine = *reinterpret_cast<const float2*>(p.rope_cs + (static_cast<size_t>(tf) * 32 + lane) * 2);
+    const float4* t = reinterpret_cast<const float4*>(p.rope_cs + (static_cast<size_t>(tf) * 32 + 4 * part) * 2);
+    const float4 a = t[0], b = t[1];
+    cs[0] = make_float2(a.x, a.y);
+    cs[1] = make_float2(a.z, a.w);
+    cs[2] = make_float2(b.x, b.y);
+    cs[3] = make_float2(b.z, b.w);
   } else if (p.rope_mode == GCT_ROPE_2D) {
-    const int half = lane >> 4;                 // elements 2m,2m+1 < 32 -> vertical half, else horizontal
-    const int j0 = (2 * lane) & 15;             // angle index inside the half for element 2m
-    cs_mine = *reinterpret_cast<const float2*>(p.rope_cs + (static_cast<size_t>(tf) * 32 + half * 16 + j0) * 2);
-    cs_2d = *reinterpret_cast<const float2*>(p.rope_cs + (static_cast<size_t>(tf) * 32 + half * 16 + j0 + 1) * 2);
+    const int entry = (part >> 2) * 16 + (part & 1) * 8;      // 16*half + (e' % 16) for this lane's first element
+    const float4* t = reinterpret_cast<const float4*>(p.rope_cs + (static_cast<size_t>(tf) * 32 + entry) * 2);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 a = t[i];
+      cs[2 * i] = make_float2(a.x, a.y);
+      cs[2 * i + 1] = make_float2(a.z, a.w);
+    }
   }
 
   // destination rows of K and V for this token
@@ -108,20 +162,26 @@ __global__ void __launch_bounds__(256) gct_prep_kernel(const PrepLaunch p) {
     v_row = k_row + page_elems;
   }
 
-  for (int h = h0; h < min(h0 + kHeadsPerWarp, p.heads); ++h) {
-    const size_t src = static_cast<size_t>(token) * p.src_token_stride + static_cast<size_t>(h) * p.src_head_stride +
-                       2 * lane;
-    const size_t dst = static_cast<size_t>(h) * kHeadDim + 2 * lane;
-    if (p.q_src != nullptr && p.q_out != nullptr) {
-      float2 x = norm_rope(load2(p.q_src, p.src_dtype_qk, src), p.qn_w, p.qn_b, cs_mine, cs_2d, p.rope_mode, lane);
-      *reinterpret_cast<__nv_bfloat162*>(p.q_out + static_cast<size_t>(token) * p.heads * kHeadDim + dst) =
-          __floats2bfloat162_rn(x.x, x.y);
-    }
-    if (k_row != nullptr) {
-      float2 x = norm_rope(load2(p.k_src, p.src_dtype_qk, src), p.kn_w, p.kn_b, cs_mine, cs_2d, p.rope_mode, lane);
-      *reinterpret_cast<__nv_bfloat162*>(k_row + dst) = __floats2bfloat162_rn(x.x, x.y);
-      float2 y = load2(p.v_src, p.src_dtype_v, src);
-      *reinterpret_cast<__nv_bfloat162*>(v_row + dst) = __floats2bfloat162_rn(y.x, y.y);
+  const size_t src = static_cast<size_t>(token) * p.src_token_stride + static_cast<size_t>(hh) * p.src_head_stride +
+                     8 * part;
+  const size_t dst = static_cast<size_t>(hh) * kHeadDim + 8 * part;
+  const bool do_q = p.q_src != nullptr && p.q_out != nullptr;
+  const bool do_kv = k_row != nullptr;
+  Row8 q, k, v;
+  if (do_q) q = load8(p.q_src, p.src_dtype_qk, src);
+  if (do_kv) {
+    k = load8(p.k_src, p.src_dtype_qk, src);
+    v = load8(p.v_src, p.src_dtype_v, src);
+  }
+  if (do_q) {
+    norm_rope8(q, p.qn_w, p.qn_b, cs, p.rope_mode, part);
+    if (active) store8(p.q_out + static_cast<size_t>(token) * p.heads * kHeadDim + dst, q);
+  }
+  if (do_kv) {
+    norm_rope8(k, p.kn_w, p.kn_b, cs, p.rope_mode, part);
+    if (active) {
+      store8(k_row + dst, k);
+      store8(v_row + dst, v);
     }
   }
 }
@@ -221,7 +281,13 @@ __global__ void gct_rope2d_table_kernel(int pph, int ppw, int ns, float base, fl
 int launch_prep(const PrepLaunch& p, cudaStream_t stream) {
   if (p.tokens <= 0 || p.heads <= 0 || p.tokens_per_frame <= 0) return fail(GCT_ERR_INVALID, "prep: bad shape");
   if (p.rope_mode != GCT_ROPE_NONE && p.rope_cs == nullptr) return fail(GCT_ERR_INVALID, "prep: rope table missing");
-  if ((p.src_token_stride | p.src_head_stride) & 1) return fail(GCT_ERR_INVALID, "prep: odd source stride");
+  if ((p.src_token_stride | p.src_head_stride) & 7)
+    return fail(GCT_ERR_INVALID, "prep: source strides must be multiples of 8 elements (16-byte vector loads)");
+  auto misaligned = [](const void* q) { return q != nullptr && (reinterpret_cast<uintptr_t>(q) & 15) != 0; };
+  if (misaligned(p.q_src) || misaligned(p.k_src) || misaligned(p.v_src) || misaligned(p.q_out) || misaligned(p.k_out) ||
+      misaligned(p.v_out) || misaligned(p.pool) || misaligned(p.qn_w) || misaligned(p.qn_b) || misaligned(p.kn_w) ||
+      misaligned(p.kn_b) || misaligned(p.rope_cs))
+    return fail(GCT_ERR_INVALID, "prep: tensors must be 16-byte aligned");
   const int head_groups = (p.heads + kHeadsPerWarp - 1) / kHeadsPerWarp;
   const long long warps = static_cast<long long>(p.tokens) * head_groups;
   const int blocks = static_cast<int>((warps * 32 + 255) / 256);
