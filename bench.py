@@ -134,7 +134,7 @@ class HotPath:
         self.outs = [None] * (2 * DEPTH)
         self.launches = 0
 
-    def step(self, qkv_frame=None, qkv_global=None):
+    def step(self, qkv_frame=None, qkv_global=None, before_layer=None, after_layer=None):
         P, lib, m = self.P, self.lib, self.mgr
         qkv_frame = qkv_frame or self.qkv_frame
         qkv_global = qkv_global or self.qkv_global
@@ -142,6 +142,8 @@ class HotPath:
         P.ops.rope3d_table(self.frame_index % 1024, PPH, PPW, NSPECIAL, self.dev, out=self.cs3d)
         self.launches += 1
         for b in range(DEPTH):
+            if before_layer is not None:
+                before_layer(b)
             q, k, v = P.ops.prep_qkv(qkv_frame[b], HEADS, TPF, *self.norm[2 * b], self.cs2d, lib.ROPE_2D)
             self.outs[2 * b] = P.ops.dense_attention(q[None], k[None], v[None])
             qg = m.append_frame_fused(b, qkv_global[b], *self.norm[2 * b + 1], self.cs3d, lib.ROPE_3D)
@@ -153,6 +155,8 @@ class HotPath:
                 from lingbot_map_b200 import distributed as D
                 self.outs[2 * b + 1] = D.sharded_attention(m, b, qg, *self.shard)
                 self.launches += 6          # ... + the cross-rank merge
+            if after_layer is not None:
+                after_layer(b)
         self.frame_index += 1
 
 
@@ -215,13 +219,43 @@ def run_gpu(args):
     d_in_f = [torch.empty(TPF, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)]
     d_in_g = [torch.empty(TPF, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)]
 
-    def e2e_step():
-        for b in range(DEPTH):
+    # Copies run on their own stream, one layer ahead of / behind the compute stream: the inputs of layer b
+    # are uploaded while layer b-1 computes, and the outputs of layer b are downloaded while layer b+1
+    # computes.  Events order every buffer hand-over in both directions.
+    copy_stream = torch.cuda.Stream(device=dev)
+    main_stream = torch.cuda.current_stream(dev)
+    ev_in = [torch.cuda.Event() for _ in range(DEPTH)]       # inputs of layer b are on the device
+    ev_free = [torch.cuda.Event() for _ in range(DEPTH)]     # layer b no longer reads its input buffers
+    ev_out = [torch.cuda.Event() for _ in range(DEPTH)]      # outputs of layer b are computed
+    for e in ev_free:
+        e.record(main_stream)
+
+    def upload(b):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(ev_free[b])
             d_in_f[b].copy_(h_in_f[b], non_blocking=True)
             d_in_g[b].copy_(h_in_g[b], non_blocking=True)
-        hp.step(d_in_f, d_in_g)
-        for i in range(2 * DEPTH):
-            h_out[i].copy_(hp.outs[i].view(TPF, HEADS, HEAD_DIM), non_blocking=True)
+            ev_in[b].record(copy_stream)
+
+    def before_layer(b):
+        if b == 0:
+            upload(0)
+        if b + 1 < DEPTH:
+            upload(b + 1)
+        main_stream.wait_event(ev_in[b])
+
+    def after_layer(b):
+        ev_free[b].record(main_stream)
+        ev_out[b].record(main_stream)
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(ev_out[b])
+            for i in (2 * b, 2 * b + 1):
+                hp.outs[i].record_stream(copy_stream)
+                h_out[i].copy_(hp.outs[i].view(TPF, HEADS, HEAD_DIM), non_blocking=True)
+
+    def e2e_step():
+        hp.step(d_in_f, d_in_g, before_layer, after_layer)
+        main_stream.wait_stream(copy_stream)                 # the step ends when its results are on the host
 
     e2e_step()
     barrier()
