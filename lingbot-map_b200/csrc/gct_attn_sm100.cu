@@ -171,6 +171,24 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x for two logits on the FMA pipe instead of the special-function unit: clamp to >= -125, split
+// x = n + f with n = round(x) (adding 1.5 * 2^23 leaves n in the low mantissa bits), 2^f on [-0.5, 0.5] by a
+// degree-3 polynomial (relative error 7.5e-5, far below bf16 resolution), then n is added to the exponent.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  constexpr float kMagic = 12582912.f;
+  x.x = fmaxf(x.x, -125.f);
+  x.y = fmaxf(x.y, -125.f);
+  const float2 t = __fadd2_rn(x, make_float2(kMagic, kMagic));
+  const float2 n = __fadd2_rn(t, make_float2(-kMagic, -kMagic));
+  const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
+  float2 p = __ffma2_rn(make_float2(0.0551716648f, 0.0551716648f), f, make_float2(0.2426111251f, 0.2426111251f));
+  p = __ffma2_rn(p, f, make_float2(0.6932609677f, 0.6932609677f));
+  p = __ffma2_rn(p, f, make_float2(0.9999280572f, 0.9999280572f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -195,6 +213,10 @@ struct KernelArgs {
 
 constexpr int kKStages = 4;
 constexpr int kVStages = 4;
+#ifndef GCT_POLY_EVERY
+#define GCT_POLY_EVERY 4
+#endif
+constexpr int kPolyEvery = GCT_POLY_EVERY;   // 0: all exponentials on the special-function unit
 constexpr float kRescaleThreshold = 8.0f;   // in log2 units of the scaled logits
 
 template <int QT>
@@ -380,6 +402,34 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     for (int j = 0; j < nblk; ++j) {
       if (!(ok = mbar_wait(bar_s_full(t), j & 1, cta_abort, a.status))) break;
       tc_fence_after();
+      // valid tokens of this block
+      const int g = g0 + j;
+      const int pi = g / a.blocks_per_page;
+      const int jb = g - pi * a.blocks_per_page;
+      const int plen = (pi == a.n_pages - 1) ? a.last_page_len : a.page_len;
+      const int valid = min(kBlockN, plen - jb * kBlockN);
+      // masked maximum of s[lo, lo+64): four independent chains of 3-input max
+      auto half_max = [&](int lo) -> float {
+        if (valid < lo + 64) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (lo + i >= valid) s[lo + i] = 0xff800000u;   // -inf: exp2 gives 0
+        }
+        float mx0 = __uint_as_float(s[lo + 0]), mx1 = __uint_as_float(s[lo + 1]), mx2 = __uint_as_float(s[lo + 2]),
+              mx3 = __uint_as_float(s[lo + 3]);
+#pragma unroll
+        for (int i = 4; i < 60; i += 8) {
+          mx0 = max3(mx0, __uint_as_float(s[lo + i + 0]), __uint_as_float(s[lo + i + 1]));
+          mx1 = max3(mx1, __uint_as_float(s[lo + i + 2]), __uint_as_float(s[lo + i + 3]));
+          mx2 = max3(mx2, __uint_as_float(s[lo + i + 4]), __uint_as_float(s[lo + i + 5]));
+          mx3 = max3(mx3, __uint_as_float(s[lo + i + 6]), __uint_as_float(s[lo + i + 7]));
+        }
+        mx0 = max3(mx0, __uint_as_float(s[lo + 60]), __uint_as_float(s[lo + 61]));
+        mx1 = max3(mx1, __uint_as_float(s[lo + 62]), __uint_as_float(s[lo + 63]));
+        return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      };
+      // the second half of the row is still arriving from TMEM while the first half is reduced
+      float mx;
       {
         uint32_t(&s0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
         uint32_t(&s1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32]);
@@ -387,40 +437,17 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint32_t(&s3)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[96]);
         tmem_ld32(s_addr, s0);
         tmem_ld32(s_addr + 32, s1);
+        tmem_wait_ld();
         tmem_ld32(s_addr + 64, s2);
         tmem_ld32(s_addr + 96, s3);
+        const float mlo = half_max(0);
         tmem_wait_ld();
+        // the S tile is in registers: the tensor core may overwrite it with the next block
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_s_empty(t));
+        mx = fmaxf(mlo, half_max(64));
       }
-      // the S tile is in registers: the tensor core may overwrite it with the next block
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_s_empty(t));
-
-      // valid tokens of this block
-      const int g = g0 + j;
-      const int pi = g / a.blocks_per_page;
-      const int jb = g - pi * a.blocks_per_page;
-      const int plen = (pi == a.n_pages - 1) ? a.last_page_len : a.page_len;
-      const int valid = min(kBlockN, plen - jb * kBlockN);
-      if (valid < kBlockN) {
-#pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (i >= valid) s[i] = 0xff800000u;   // -inf: exp2 gives 0
-      }
-
-      // row maximum, four independent chains of 3-input max
-      float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]), mx2 = __uint_as_float(s[2]),
-            mx3 = __uint_as_float(s[3]);
-#pragma unroll
-      for (int i = 4; i < 124; i += 8) {
-        mx0 = max3(mx0, __uint_as_float(s[i + 0]), __uint_as_float(s[i + 1]));
-        mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-        mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
-        mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
-      }
-      mx0 = max3(mx0, __uint_as_float(s[124]), __uint_as_float(s[125]));
-      mx1 = max3(mx1, __uint_as_float(s[126]), __uint_as_float(s[127]));
-      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       // move the reference maximum only when the row maximum outgrew it by more than 2^kRescaleThreshold;
       // until then exponentials stay below 2^8 and every sum remains exact enough in fp32
       float alpha = 1.f;
@@ -463,8 +490,16 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         s[2 * q + 1] = __float_as_uint(x.y);
       };
       auto pair_exp = [&](int q) {
-        s[2 * q] = __float_as_uint(fast_exp2(__uint_as_float(s[2 * q])));
-        s[2 * q + 1] = __float_as_uint(fast_exp2(__uint_as_float(s[2 * q + 1])));
+        if (kPolyEvery > 0 && (q % (kPolyEvery > 0 ? kPolyEvery : 1)) == (kPolyEvery - 1)) {
+          // every kPolyEvery-th pair is exponentiated on the FMA pipe: the special-function unit delivers only
+          // 16 results per clock and SM, half of what the tensor core consumes at head_dim 64
+          const float2 e = exp2_poly2(make_float2(__uint_as_float(s[2 * q]), __uint_as_float(s[2 * q + 1])));
+          s[2 * q] = __float_as_uint(e.x);
+          s[2 * q + 1] = __float_as_uint(e.y);
+        } else {
+          s[2 * q] = __float_as_uint(fast_exp2(__uint_as_float(s[2 * q])));
+          s[2 * q + 1] = __float_as_uint(fast_exp2(__uint_as_float(s[2 * q + 1])));
+        }
       };
       auto pair_sum = [&](int q) {
         const float2 e = make_float2(__uint_as_float(s[2 * q]), __uint_as_float(s[2 * q + 1]));
