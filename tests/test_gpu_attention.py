@@ -316,3 +316,52 @@ def test_sharded_records_and_strided_merge():
     o1 = D.sharded_attention(m, 1, bf(q), 0, 1)
     assert_close(o1, want, "sharded_attention world=1")
     assert o0.shape == o1.shape and m.device_status() == 0
+
+
+@pytest.mark.parametrize("q_len", [1, 6, 130, 262])
+@pytest.mark.parametrize("qdtype", ["bf16", "f32"])
+def test_paged_attention_query_lengths(q_len, qdtype):
+    """Query lengths below a full frame (the reference's wrapper takes any qo length), last special page
+    partially filled, fp32 queries cast to bf16 like flashinfer_cache.py:419."""
+    tpf, H = 262, 2                               # the reference's _sanity_check geometry: page of 256 tokens
+    m = P.B200KVCacheManager(1, 30, tpf, H, 64, device=DEV, scale_frames=2, sliding_window=4, max_total_frames=100)
+    orc = O.PagedCacheOracle(1, tpf, H, 64, scale_frames=2, sliding_window=4, max_total_frames=100)
+    for t in range(11):
+        k, v = seeded.randn(300 + t, tpf, H, 64), seeded.randn(400 + t, tpf, H, 64)
+        m.append_frame(0, bf(k), bf(v))
+        m.evict_frames(0, 2, 4)
+        orc.append_frame(0, r(k), r(v))
+        orc.evict_frames(0, 2, 4)
+    q = seeded.randn(555, q_len, H, 64)
+    qd = bf(q) if qdtype == "bf16" else torch.from_numpy(q).to(DEV)
+    m.plan()
+    out = torch.empty(q_len, H, 64, dtype=torch.bfloat16, device=DEV)
+    _lib.check(m._lib.gct_mgr_attention(m._handle, 0, qd.data_ptr(), _lib.BF16 if qdtype == "bf16" else _lib.F32, q_len,
+                                        out.data_ptr(), None, torch.cuda.current_stream().cuda_stream))
+    kk, vv = orc.gather_kv(0)
+    assert kk.shape[0] == 256 * 6 + 66
+    assert_close(out, O.attention(r(q), kk, vv)[0], f"q_len {q_len}")
+    assert m.device_status() == 0
+
+
+def test_argument_errors_are_reported_not_trapped():
+    m = P.B200KVCacheManager(1, 21, 26, 2, 64, device=DEV, scale_frames=2, sliding_window=3, max_total_frames=40)
+    k = torch.zeros(26, 2, 64, device=DEV)
+    m.append_frame(0, k, k)
+    lib = m._lib
+    q = torch.zeros(26, 2, 64, dtype=torch.bfloat16, device=DEV)
+    out = torch.empty_like(q)
+    s = torch.cuda.current_stream().cuda_stream
+    # no plan yet
+    assert lib.gct_mgr_attention(m._handle, 0, q.data_ptr(), _lib.BF16, 26, out.data_ptr(), None, s) == _lib.ERR_INVALID
+    assert b"plan" in lib.gct_last_error()
+    m.plan()
+    assert lib.gct_mgr_attention(m._handle, 3, q.data_ptr(), _lib.BF16, 26, out.data_ptr(), None, s) == _lib.ERR_INVALID
+    assert lib.gct_mgr_attention(m._handle, 0, q.data_ptr(), _lib.BF16, 27, out.data_ptr(), None, s) == _lib.ERR_INVALID
+    assert lib.gct_mgr_attention(m._handle, 0, q.data_ptr(), 7, 26, out.data_ptr(), None, s) == _lib.ERR_INVALID
+    assert lib.gct_mgr_plan(m._handle, 2, 1, s) == _lib.ERR_INVALID
+    with pytest.raises(TypeError):
+        m.append_frame(0, k.half(), k.half())
+    with pytest.raises(AssertionError, match="expected 20 patch tokens"):
+        m.append_frame(0, torch.zeros(25, 2, 64, device=DEV), torch.zeros(25, 2, 64, device=DEV))
+    assert m.device_status() == 0
