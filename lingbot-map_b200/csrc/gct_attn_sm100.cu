@@ -98,17 +98,33 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+// The MMA warps keep their control flow warp-uniform and predicate only the tcgen05 instructions on
+// one elected lane (`lead` != 0 in that lane).  Descriptors and addresses computed by the whole warp
+// can live in uniform registers; computed by a single lane inside a divergent branch they are moved
+// there one by one before every instruction, which limits the issue rate to one MMA per ~60-90 clocks
+// (measured), well below the 32-64 clocks an N=64/128, K=16 instruction occupies the tensor core.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t e;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(e));
+  return e;
 }
-// D[tmem] (+)= A[smem] * B[smem], bf16 x bf16 -> fp32, issued by one thread.
-__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+__device__ __forceinline__ void tc_commit_elected(uint32_t lead, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred e;\n\t"
+      "setp.ne.b32 e, %1, 0;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(bar), "r"(lead)
+      : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], bf16 x bf16 -> fp32, issued by the elected lane.
+__device__ __forceinline__ void umma_ss(uint32_t lead, uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                         uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
+      "{\n\t.reg .pred p, e;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      "setp.ne.b32 e, %5, 0;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(lead)
       : "memory");
 }
 // 32 consecutive fp32 columns of this thread's TMEM lane.
@@ -143,13 +159,14 @@ constexpr uint32_t kIdescPV =
     (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
 
 // D[tmem] (+)= A[tmem] * B[smem]: A is read from TMEM (lane = row, two bf16 per 32-bit column).
-__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+__device__ __forceinline__ void umma_ts(uint32_t lead, uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
                                         uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
+      "{\n\t.reg .pred p, e;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      "setp.ne.b32 e, %5, 0;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(lead)
       : "memory");
 }
 // 32 consecutive 32-bit columns of this thread's TMEM lane.
@@ -214,9 +231,25 @@ struct KernelArgs {
 constexpr int kKStages = 4;
 constexpr int kVStages = 4;
 #ifndef GCT_POLY_EVERY
-#define GCT_POLY_EVERY 4
+#define GCT_POLY_EVERY 3
 #endif
 constexpr int kPolyEvery = GCT_POLY_EVERY;   // 0: all exponentials on the special-function unit
+#ifndef GCT_FFMA_AHEAD
+#define GCT_FFMA_AHEAD 4
+#endif
+#ifndef GCT_SUM_LAG
+#define GCT_SUM_LAG 2
+#endif
+constexpr int kFfmaAhead = GCT_FFMA_AHEAD;   // software pipeline of the exponential sweep, in pairs of logits
+constexpr int kSumLag = GCT_SUM_LAG;
+#ifndef GCT_MAX_CHAINS
+#define GCT_MAX_CHAINS 4
+#endif
+#ifndef GCT_PV_WAIT_AT
+#define GCT_PV_WAIT_AT 31
+#endif
+constexpr int kPvWaitAt = GCT_PV_WAIT_AT;    // pair (31..61) after which the sweep waits for the previous PV and stores P[0,64)
+constexpr int kMaxChains = GCT_MAX_CHAINS;   // power of two, independent dependency chains of the row maximum
 constexpr float kRescaleThreshold = 8.0f;   // in log2 units of the scaled logits
 
 template <int QT>
@@ -343,46 +376,51 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // =========================== MMA issuer of tile t ===========================
     if constexpr (QT == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
     const int t = warp - kFirstMmaWarp;
-    if (lane == 0 && t < QT) {
+    if (t < QT) {
+      // all 32 lanes run the loop and the waits; `lead` marks the lane that issues
+      const uint32_t lead = elect_one();
       auto issue_s = [&](int ks) {
         const uint64_t ad = smem_desc(sbase + L::q_off + t * kTileBytes, 16, 1024);
         const uint64_t bd = smem_desc(sbase + L::k_off + ks * kTileBytes, 16, 1024);
 #pragma unroll
         for (int k = 0; k < 4; ++k)   // 64 = 4 x K16; +32 B per step inside the 128 B swizzle row
-          umma_ss(tmem_base + t * 128, ad + 2 * k, bd + 2 * k, kIdescS, k > 0);
+          umma_ss(lead, tmem_base + t * 128, ad + 2 * k, bd + 2 * k, kIdescS, k > 0);
       };
       auto issue_pv = [&](int vs, uint32_t accumulate) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) {   // 128 tokens = 8 x K16: 8 TMEM columns of P and 16 V rows per step
           const uint64_t bd = smem_desc(sbase + L::v_off + vs * kTileBytes + k * 2048, 16, 1024);
-          umma_ts(tmem_base + kOCol + t * 64, tmem_base + kPCol + t * 64 + k * 8, bd, kIdescPV,
+          umma_ts(lead, tmem_base + kOCol + t * 64, tmem_base + kPCol + t * 64 + k * 8, bd, kIdescPV,
                   (k > 0) ? 1u : accumulate);
         }
       };
-      bool ok = mbar_wait(bar_q_full(), 0, cta_abort, a.status) && mbar_wait(bar_k_full(0), 0, cta_abort, a.status);
+      auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, cta_abort, a.status));
+      };
+      bool ok = wait(bar_q_full(), 0) && wait(bar_k_full(0), 0);
       if (ok) {
         tc_fence_after();
         issue_s(0);
-        tc_commit(bar_s_full(t));
-        tc_commit(bar_k_empty(0));
+        tc_commit_elected(lead, bar_s_full(t));
+        tc_commit_elected(lead, bar_k_empty(0));
       }
       for (int j = 0; ok && j < nblk; ++j) {
         if (j + 1 < nblk) {
           const int ks = (j + 1) % kKStages;
-          if (!(ok = mbar_wait(bar_s_empty(t), j & 1, cta_abort, a.status))) break;
-          if (!(ok = mbar_wait(bar_k_full(ks), ((j + 1) / kKStages) & 1, cta_abort, a.status))) break;
+          if (!(ok = wait(bar_s_empty(t), j & 1))) break;
+          if (!(ok = wait(bar_k_full(ks), ((j + 1) / kKStages) & 1))) break;
           tc_fence_after();
           issue_s(ks);
-          tc_commit(bar_s_full(t));
-          tc_commit(bar_k_empty(ks));
+          tc_commit_elected(lead, bar_s_full(t));
+          tc_commit_elected(lead, bar_k_empty(ks));
         }
         const int vs = j % kVStages;
-        if (!(ok = mbar_wait(bar_p_full(t), j & 1, cta_abort, a.status))) break;
-        if (!(ok = mbar_wait(bar_v_full(vs), (j / kVStages) & 1, cta_abort, a.status))) break;
+        if (!(ok = wait(bar_p_full(t), j & 1))) break;
+        if (!(ok = wait(bar_v_full(vs), (j / kVStages) & 1))) break;
         tc_fence_after();
         issue_pv(vs, j > 0 ? 1u : 0u);
-        tc_commit(bar_pv_full(t));
-        tc_commit(bar_v_empty(vs));
+        tc_commit_elected(lead, bar_pv_full(t));
+        tc_commit_elected(lead, bar_v_empty(vs));
       }
     }
   } else {
@@ -399,15 +437,18 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     bool ok = true;
     uint32_t s[128];
 
+    int pi = g0 / a.blocks_per_page;               // page and block-in-page of block j, advanced incrementally
+    int jb = g0 - pi * a.blocks_per_page;
     for (int j = 0; j < nblk; ++j) {
       if (!(ok = mbar_wait(bar_s_full(t), j & 1, cta_abort, a.status))) break;
       tc_fence_after();
       // valid tokens of this block
-      const int g = g0 + j;
-      const int pi = g / a.blocks_per_page;
-      const int jb = g - pi * a.blocks_per_page;
       const int plen = (pi == a.n_pages - 1) ? a.last_page_len : a.page_len;
       const int valid = min(kBlockN, plen - jb * kBlockN);
+      if (++jb == a.blocks_per_page) {
+        jb = 0;
+        ++pi;
+      }
       // masked maximum of s[lo, lo+64): four independent chains of 3-input max
       auto half_max = [&](int lo) -> float {
         if (valid < lo + 64) {
@@ -415,18 +456,31 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           for (int i = 0; i < 64; ++i)
             if (lo + i >= valid) s[lo + i] = 0xff800000u;   // -inf: exp2 gives 0
         }
-        float mx0 = __uint_as_float(s[lo + 0]), mx1 = __uint_as_float(s[lo + 1]), mx2 = __uint_as_float(s[lo + 2]),
-              mx3 = __uint_as_float(s[lo + 3]);
+        // kMaxChains independent chains of 3-input max, merged by a tree at the end
+        float mxc[kMaxChains];
 #pragma unroll
-        for (int i = 4; i < 60; i += 8) {
-          mx0 = max3(mx0, __uint_as_float(s[lo + i + 0]), __uint_as_float(s[lo + i + 1]));
-          mx1 = max3(mx1, __uint_as_float(s[lo + i + 2]), __uint_as_float(s[lo + i + 3]));
-          mx2 = max3(mx2, __uint_as_float(s[lo + i + 4]), __uint_as_float(s[lo + i + 5]));
-          mx3 = max3(mx3, __uint_as_float(s[lo + i + 6]), __uint_as_float(s[lo + i + 7]));
+        for (int ch = 0; ch < kMaxChains; ++ch) mxc[ch] = __uint_as_float(s[lo + ch]);
+        constexpr int kRounds = (64 - kMaxChains) / (2 * kMaxChains);   // full rounds of one max3 per chain
+#pragma unroll
+        for (int r = 0; r < kRounds; ++r)
+#pragma unroll
+          for (int ch = 0; ch < kMaxChains; ++ch) {
+            const int i = kMaxChains + 2 * (r * kMaxChains + ch);
+            mxc[ch] = max3(mxc[ch], __uint_as_float(s[lo + i]), __uint_as_float(s[lo + i + 1]));
+          }
+        {
+          constexpr int kDone = kMaxChains + 2 * kRounds * kMaxChains;   // elements consumed so far
+#pragma unroll
+          for (int i = kDone; i < 64; i += 2) {
+            const int ch = ((i - kDone) / 2) % kMaxChains;
+            mxc[ch] = max3(mxc[ch], __uint_as_float(s[lo + i]), __uint_as_float(s[lo + i + 1]));
+          }
         }
-        mx0 = max3(mx0, __uint_as_float(s[lo + 60]), __uint_as_float(s[lo + 61]));
-        mx1 = max3(mx1, __uint_as_float(s[lo + 62]), __uint_as_float(s[lo + 63]));
-        return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+#pragma unroll
+        for (int w = kMaxChains / 2; w >= 1; w /= 2)
+#pragma unroll
+          for (int ch = 0; ch < w; ++ch) mxc[ch] = fmaxf(mxc[ch], mxc[ch + w]);
+        return mxc[0];
       };
       // the second half of the row is still arriving from TMEM while the first half is reduced
       float mx;
@@ -437,6 +491,13 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint32_t(&s3)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[96]);
         tmem_ld32(s_addr, s0);
         tmem_ld32(s_addr + 32, s1);
+        if (j > 0) {
+          // P of the previous block: its stores completed while the loads above were issued
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_p_full(t));
+        }
         tmem_wait_ld();
         tmem_ld32(s_addr + 64, s2);
         tmem_ld32(s_addr + 96, s3);
@@ -483,7 +544,7 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // pair p-2 its packed add into the row sum and its bf16 conversion (two K values per TMEM column).
       const float2 c2 = make_float2(c, c), nmc2 = make_float2(-mc, -mc);
       float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
-      uint32_t pk[32];
+      uint32_t pk[kPvWaitAt > 31 ? 64 : 32];
       auto pair_ffma = [&](int q) {
         const float2 x = __ffma2_rn(make_float2(__uint_as_float(s[2 * q]), __uint_as_float(s[2 * q + 1])), c2, nmc2);
         s[2 * q] = __float_as_uint(x.x);
@@ -504,32 +565,34 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       auto pair_sum = [&](int q) {
         const float2 e = make_float2(__uint_as_float(s[2 * q]), __uint_as_float(s[2 * q + 1]));
         if (q & 1) acc1 = __fadd2_rn(acc1, e); else acc0 = __fadd2_rn(acc0, e);
-        pk[q & 31] = pack_bf16x2(e.x, e.y);
+        pk[kPvWaitAt > 31 ? q : (q & 31)] = pack_bf16x2(e.x, e.y);
       };
 #pragma unroll
-      for (int q = 0; q < 4; ++q) pair_ffma(q);
+      for (int q = 0; q < kFfmaAhead; ++q) pair_ffma(q);
 #pragma unroll
       for (int q = 0; q < 64; ++q) {
-        if (q + 4 < 64) pair_ffma(q + 4);
+        if (q + kFfmaAhead < 64) pair_ffma(q + kFfmaAhead);
         pair_exp(q);
-        if (q >= 2) {
-          pair_sum(q - 2);
-          if (q - 2 == 31) {                            // first 64 keys done
+        if (q >= kSumLag) {
+          pair_sum(q - kSumLag);
+          if (q - kSumLag == kPvWaitAt) {               // at least the first 64 keys are done
             ok = wait_prev_pv_and_rescale();
-            if (ok) tmem_st32(p_addr, pk);
+            if (ok) tmem_st32(p_addr, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
           }
         }
       }
-      pair_sum(62);
-      pair_sum(63);
+#pragma unroll
+      for (int q = 64 - kSumLag; q < 64; ++q) pair_sum(q);
       if (!ok) break;
-      tmem_st32(p_addr + 32, pk);
+      tmem_st32(p_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[kPvWaitAt > 31 ? 32 : 0]));
       const float rs0 = acc0.x, rs1 = acc0.y, rs2 = acc1.x, rs3 = acc1.y;
       l = fmaf(l, alpha, (rs0 + rs1) + (rs2 + rs3));
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p_full(t));
+      if (j + 1 == nblk) {                          // otherwise the next iteration announces P after its first loads
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_p_full(t));
+      }
     }
 
     // ---- epilogue: O / l ----
