@@ -249,7 +249,19 @@ constexpr int kSumLag = GCT_SUM_LAG;
 #define GCT_PV_WAIT_AT 31
 #endif
 constexpr int kPvWaitAt = GCT_PV_WAIT_AT;    // pair (31..61) after which the sweep waits for the previous PV and stores P[0,64)
-constexpr int kMaxChains = GCT_MAX_CHAINS;   // power of two, independent dependency chains of the row maximum
+constexpr int kMaxChains = GCT_MAX_CHAINS;
+// Register budget at two query tiles per CTA: 384 threads start with 168 registers each (64512 in total);
+// the control warpgroup shrinks to kControlRegs and the two softmax warpgroups grow to kSoftmaxRegs:
+// 128 * kControlRegs + 256 * kSoftmaxRegs <= 64512, both multiples of 8.
+#ifndef GCT_CONTROL_REGS
+#define GCT_CONTROL_REGS 64
+#endif
+#ifndef GCT_SOFTMAX_REGS
+#define GCT_SOFTMAX_REGS 208
+#endif
+constexpr int kControlRegs = GCT_CONTROL_REGS;
+constexpr int kSoftmaxRegs = GCT_SOFTMAX_REGS;
+static_assert(128 * kControlRegs + 256 * kSoftmaxRegs <= 64512, "register pool of the CTA exceeded");   // power of two, independent dependency chains of the row maximum
 constexpr float kRescaleThreshold = 8.0f;   // in log2 units of the scaled logits
 
 template <int QT>
@@ -349,7 +361,7 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // share to the two softmax warpgroups, whose threads hold a whole 128-column S row.
   if (warp == kProducerWarp) {
     // =========================== producer ===========================
-    if constexpr (QT == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    if constexpr (QT == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
     if (lane == 0) {
       mbar_arrive_expect_tx(bar_q_full(), QT * kTileBytes);
       for (int t = 0; t < QT; ++t)
@@ -374,7 +386,7 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else if (warp >= kFirstMmaWarp) {
     // =========================== MMA issuer of tile t ===========================
-    if constexpr (QT == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    if constexpr (QT == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
     const int t = warp - kFirstMmaWarp;
     if (t < QT) {
       // all 32 lanes run the loop and the waits; `lead` marks the lane that issues
@@ -425,7 +437,7 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else {
     // =========================== softmax ===========================
-    if constexpr (QT == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    if constexpr (QT == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
     const int t = warp >> 2;                       // query tile of this warp
     const int row = ((warp & 3) << 5) | lane;      // row inside the tile == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) << 5) << 16;

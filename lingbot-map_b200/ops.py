@@ -1,6 +1,11 @@
 """Stand-alone operators of the B200 backend (thin wrappers over the C ABI): dense attention for the
 frame blocks and the phase-1 scale pass, the fused q/k-norm + RoPE + bf16 prologue, RoPE tables and the
-log-sum-exp merge of partial attention results.  All of them need a CUDA device."""
+log-sum-exp merge of partial attention results.  All of them need a CUDA device.
+
+Dense attention and the prologue are also registered as torch.library custom operators
+(`gct_b200::dense_attention`, `gct_b200::prep_qkv`) with shape-only fake implementations: the reference
+wraps whole frame blocks and `attn_pre` in torch.compile (demo.py:177-186, gct_profile.py:47-57), and a
+custom operator is traced as one opaque node instead of breaking the graph at the ctypes call."""
 import ctypes as C
 from typing import Optional
 
@@ -33,6 +38,12 @@ def dense_attention(q: Tensor, k: Tensor, v: Tensor, out: Optional[Tensor] = Non
 
     q [B, Nq, H, 64], k/v [B, Nkv, H, 64] bf16 with arbitrary strides (head_dim contiguous, strides
     multiples of 8 elements) -> [B, Nq, H, 64] bf16 contiguous."""
+    if out is None:
+        return torch.ops.gct_b200.dense_attention(q, k, v)
+    return _dense_attention_impl(q, k, v, out)
+
+
+def _dense_attention_impl(q: Tensor, k: Tensor, v: Tensor, out: Optional[Tensor] = None) -> Tensor:
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _require_cuda(t, n)
         if t.dtype != torch.bfloat16 or t.dim() != 4 or t.shape[-1] != 64 or t.stride(-1) != 1:
@@ -58,6 +69,12 @@ def prep_qkv(qkv: Tensor, heads: int, tokens_per_frame: int, q_norm_w, q_norm_b,
     """qkv Linear output [tokens, 3*H*64] -> (q, k, v) bf16 [tokens, H, 64]: LayerNorm(64) on q and k,
     RoPE from the per-token cos/sin table (indexed by token % tokens_per_frame), v cast only
     (lingbot_map/layers/attention.py:67-73)."""
+    return torch.ops.gct_b200.prep_qkv(qkv, heads, tokens_per_frame, q_norm_w, q_norm_b, k_norm_w, k_norm_b, rope_cs,
+                                       rope_mode)
+
+
+def _prep_qkv_impl(qkv: Tensor, heads: int, tokens_per_frame: int, q_norm_w, q_norm_b, k_norm_w, k_norm_b,
+                   rope_cs: Optional[Tensor], rope_mode: int):
     _require_cuda(qkv, "qkv")
     if qkv.dim() != 2 or qkv.shape[1] != 3 * heads * 64:
         raise ValueError("qkv must be [tokens, 3*H*64]")
@@ -72,6 +89,29 @@ def prep_qkv(qkv: Tensor, heads: int, tokens_per_frame: int, q_norm_w, q_norm_b,
             ptr(k_norm_w), ptr(k_norm_b), ptr(rope_cs), rope_mode, q.data_ptr(), k.data_ptr(), v.data_ptr(),
             _stream_ptr(qkv.device)))
     return q, k, v
+
+
+@torch.library.custom_op("gct_b200::dense_attention", mutates_args=())
+def _dense_attention_op(q: Tensor, k: Tensor, v: Tensor) -> Tensor:
+    return _dense_attention_impl(q, k, v, None)
+
+
+@_dense_attention_op.register_fake
+def _dense_attention_fake(q: Tensor, k: Tensor, v: Tensor) -> Tensor:
+    return q.new_empty((q.shape[0], q.shape[1], q.shape[2], 64), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("gct_b200::prep_qkv", mutates_args=())
+def _prep_qkv_op(qkv: Tensor, heads: int, tokens_per_frame: int, q_norm_w: Optional[Tensor], q_norm_b: Optional[Tensor],
+                 k_norm_w: Optional[Tensor], k_norm_b: Optional[Tensor], rope_cs: Optional[Tensor],
+                 rope_mode: int) -> tuple[Tensor, Tensor, Tensor]:
+    return _prep_qkv_impl(qkv, heads, tokens_per_frame, q_norm_w, q_norm_b, k_norm_w, k_norm_b, rope_cs, rope_mode)
+
+
+@_prep_qkv_op.register_fake
+def _prep_qkv_fake(qkv, heads, tokens_per_frame, q_norm_w, q_norm_b, k_norm_w, k_norm_b, rope_cs, rope_mode):
+    mk = lambda: qkv.new_empty((qkv.shape[0], heads, 64), dtype=torch.bfloat16)
+    return mk(), mk(), mk()
 
 
 def rope3d_table(frame_index: int, pph: int, ppw: int, num_special: int, device, out: Optional[Tensor] = None) -> Tensor:

@@ -10,6 +10,8 @@ block.py:42), so they are converted after construction with convert_frame_attent
 """
 import os
 
+_saved = {}
+
 
 def install(frame_attention: bool = True) -> None:
     """Rebind the reference's class names to the B200 implementations.  Call before building GCTStream."""
@@ -18,6 +20,9 @@ def install(frame_attention: bool = True) -> None:
     from .block import B200Block
     from .cache import B200KVCacheManager
 
+    if not _saved:
+        _saved.update(manager=cache_mod.FlashInferKVCacheManager, block=stream_mod.FlashInferBlock,
+                      init=stream_mod.AggregatorStream.__init__)
     cache_mod.FlashInferKVCacheManager = B200KVCacheManager
     stream_mod.FlashInferBlock = B200Block
     if frame_attention:
@@ -31,6 +36,19 @@ def install(frame_attention: bool = True) -> None:
 
             cls.__init__ = wrapped_init
             cls._b200_wrapped = True
+
+
+def uninstall() -> None:
+    """Undo install(): models built afterwards use the reference's own FlashInfer classes again."""
+    if not _saved:
+        return
+    import lingbot_map.aggregator.stream as stream_mod
+    import lingbot_map.layers.flashinfer_cache as cache_mod
+    cache_mod.FlashInferKVCacheManager = _saved["manager"]
+    stream_mod.FlashInferBlock = _saved["block"]
+    stream_mod.AggregatorStream.__init__ = _saved["init"]
+    stream_mod.AggregatorStream._b200_wrapped = False
+    _saved.clear()
 
 
 def convert_frame_attention(aggregator) -> int:

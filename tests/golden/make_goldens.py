@@ -289,12 +289,54 @@ def block_stream_values():
           max(float(np.abs(out[f'paged_kf1_frame{i}'] - out[f'sdpa_kf1_frame{i}']).max()) for i in range(2, 10)))
 
 
+MODEL_E2E = dict(height=126, width=182, frames=8, scale_frames=2, window=3, weight_seed=7, image_seed=5,
+                 depth_stride=7)
+
+
+def model_e2e_images():
+    c = MODEL_E2E
+    return np.random.RandomState(c["image_seed"]).rand(c["frames"], 3, c["height"], c["width"]).astype(np.float32)
+
+
+def model_e2e_values():
+    """The whole GCTStream model (models/gct_stream.py:350-470) with seeded weights, fp32 on CPU, streaming 8
+    frames (2 scale frames, then one by one): the SDPA backend with keyframe interval 1, and the paged manager's
+    fp32 gather+SDPA path (kv_cache_force_fp32) with keyframe interval 2.  Stores camera encodings and a strided
+    sample of the depth maps."""
+    import torch
+    from lingbot_map.models.gct_stream import GCTStream
+    c = MODEL_E2E
+    kw = dict(img_size=518, patch_size=14, enable_3d_rope=True, max_frame_num=64,
+              kv_cache_sliding_window=c["window"], kv_cache_scale_frames=c["scale_frames"], camera_num_iterations=4)
+    imgs = torch.from_numpy(model_e2e_images())
+    out = {}
+    for tag, use_sdpa, kf in (("sdpa_kf1", True, 1), ("paged_kf2", False, 2), ("paged_kf1", False, 1)):
+        model = GCTStream(use_sdpa=use_sdpa, **kw).eval()
+        seeded.fill_model_(model, c["weight_seed"])
+        if not use_sdpa:
+            model.aggregator.kv_cache_force_fp32 = True
+        with torch.no_grad():
+            pred = model.inference_streaming(imgs, num_scale_frames=c["scale_frames"], keyframe_interval=kf)
+        st = c["depth_stride"]
+        out[f"{tag}_pose_enc"] = pred["pose_enc"][0].numpy().astype(np.float32)
+        out[f"{tag}_depth"] = pred["depth"][0, :, ::st, ::st, 0].numpy().astype(np.float32)
+        out[f"{tag}_depth_mean"] = pred["depth"][0].mean(dim=(1, 2, 3)).numpy().astype(np.float32)
+        del model
+    np.savez_compressed(os.path.join(HERE, "model_e2e_fp32.npz"), **out)
+    print("model_e2e_fp32.npz:", {k: v.shape for k, v in out.items()})
+    print("  max |paged_kf1 - sdpa_kf1| pose:", float(np.abs(out["paged_kf1_pose_enc"] - out["sdpa_kf1_pose_enc"]).max()),
+          "depth:", float(np.abs(out["paged_kf1_depth"] - out["sdpa_kf1_depth"]).max()))
+    print("  max |paged_kf2 - sdpa_kf1| pose:", float(np.abs(out["paged_kf2_pose_enc"] - out["sdpa_kf1_pose_enc"]).max()))
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only", default="", help="comma-separated fixture names (default: all)")
     args = ap.parse_args()
     _import_reference(args.reference)
-    manager_traces()
-    paged_attention_values()
-    prepare_qkv_values()
-    block_stream_values()
+    todo = {"manager_traces": manager_traces, "paged_attention": paged_attention_values,
+            "prepare_qkv": prepare_qkv_values, "block_stream": block_stream_values, "model_e2e": model_e2e_values}
+    for name, fn in todo.items():
+        if not args.only or name in args.only.split(","):
+            fn()

@@ -1,0 +1,74 @@
+"""End-to-end drop-in check on the GPU: the reference's own GCTStream model (aggregator, camera head, depth head),
+built from an installed copy of the reference package with the B200 backend selected, against camera encodings and
+depth recorded from the reference on CPU in fp32 (tests/golden/model_e2e_fp32.npz, made by make_goldens.py).
+
+The reference package is looked for in baseline/_ref (python -m pip install --no-deps --target baseline/_ref
+<reference checkout>); without it the test is skipped.  Weights and images are regenerated from seeds.
+
+Tolerances (the model runs its Linear layers in fp32; q, k, v and the softmax weights are rounded to bf16 inside the
+attention kernels of 48 blocks): camera encoding max-abs 5e-2 (values are O(1..5)), depth max-abs 5e-2 on values
+O(1), both far below the differences between frames (O(0.5)) and between keyframe schedules (0.28)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import seeded
+import lingbot_map_b200 as P
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "baseline", "_ref")
+G = os.path.join(os.path.dirname(__file__), "golden")
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lingbot_map")),
+                                 reason="reference package not installed under baseline/_ref")]
+
+CFG = dict(height=126, width=182, frames=8, scale_frames=2, window=3, weight_seed=7, image_seed=5, depth_stride=7)
+
+
+@pytest.fixture(scope="module")
+def model():
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    from lingbot_map.models.gct_stream import GCTStream
+    P.select.install()
+    try:
+        m = GCTStream(img_size=518, patch_size=14, enable_3d_rope=True, max_frame_num=64,
+                      kv_cache_sliding_window=CFG["window"], kv_cache_scale_frames=CFG["scale_frames"],
+                      camera_num_iterations=4, use_sdpa=False).eval()
+        seeded.fill_model_(m, CFG["weight_seed"])
+        m = m.to("cuda:0")
+        assert all(isinstance(b, P.B200Block) for b in m.aggregator.global_blocks)
+        assert all(isinstance(b.attn, P.B200FrameAttention) for b in m.aggregator.frame_blocks)
+        yield m
+    finally:
+        P.select.uninstall()
+
+
+def images():
+    c = CFG
+    x = np.random.RandomState(c["image_seed"]).rand(c["frames"], 3, c["height"], c["width"]).astype(np.float32)
+    return torch.from_numpy(x).to("cuda:0")
+
+
+@pytest.mark.parametrize("tag,kf", [("paged_kf1", 1), ("paged_kf2", 2)])
+def test_streaming_poses_and_depth_match_reference(model, tag, kf):
+    z = np.load(os.path.join(G, "model_e2e_fp32.npz"))
+    model.clean_kv_cache()
+    with torch.no_grad():
+        pred = model.inference_streaming(images(), num_scale_frames=CFG["scale_frames"], keyframe_interval=kf)
+    mgr = model.aggregator.kv_cache_manager
+    assert isinstance(mgr, P.B200KVCacheManager)
+    st = CFG["depth_stride"]
+    pose = pred["pose_enc"][0].float().cpu().numpy()
+    depth = pred["depth"][0, :, ::st, ::st, 0].float().cpu().numpy()
+    dp = float(np.abs(pose - z[f"{tag}_pose_enc"]).max())
+    dd = float(np.abs(depth - z[f"{tag}_depth"]).max())
+    print(f"{tag}: pose max-abs {dp:.3e}, depth max-abs {dd:.3e}")
+    assert np.isfinite(pose).all() and np.isfinite(depth).all()
+    assert dp <= 5e-2, f"camera encoding differs by {dp}"
+    assert dd <= 5e-2, f"depth differs by {dd}"
+    assert mgr.device_status() == 0
