@@ -68,12 +68,13 @@ def main(argv=None):
     ap.add_argument("--img-h", type=int, default=378)
     ap.add_argument("--img-w", type=int, default=518)
     ap.add_argument("--no-compile", action="store_true")
+    ap.add_argument("--patch-embed", action="store_true", help="b200 backend: also convert the DINOv2 patch-embed attention")
     args = ap.parse_args(argv)
 
     gp = _load_profile_module(os.path.abspath(args.reference))
     if args.backend == "b200":
         from . import select
-        select.install()
+        select.install(patch_embed_attention=args.patch_embed)
     torch.manual_seed(0)
     model = gp.load_model("flashinfer", img_size=518, sliding_window=64, max_frame_num=args.cached_frames + 400,
                           camera_num_iterations=4)

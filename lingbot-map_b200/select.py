@@ -13,8 +13,14 @@ import os
 _saved = {}
 
 
-def install(frame_attention: bool = True) -> None:
-    """Rebind the reference's class names to the B200 implementations.  Call before building GCTStream."""
+def install(frame_attention: bool = True, patch_embed_attention: bool = None) -> None:
+    """Rebind the reference's class names to the B200 implementations.  Call before building GCTStream.
+
+    frame_attention: convert the aggregator's per-frame blocks.  patch_embed_attention: also convert the 24
+    attention layers of the DINOv2 patch embed (vision_transformer.py:144-171; plain attention over 1004 tokens,
+    no q/k norm, no RoPE); default from LINGBOT_B200_PATCH_EMBED (off unless set to 1)."""
+    if patch_embed_attention is None:
+        patch_embed_attention = os.environ.get("LINGBOT_B200_PATCH_EMBED", "0") == "1"
     import lingbot_map.aggregator.stream as stream_mod
     import lingbot_map.layers.flashinfer_cache as cache_mod
     from .block import B200Block
@@ -32,7 +38,7 @@ def install(frame_attention: bool = True) -> None:
 
             def wrapped_init(self, *args, **kwargs):
                 orig_init(self, *args, **kwargs)
-                convert_frame_attention(self)
+                convert_frame_attention(self, patch_embed=patch_embed_attention)
 
             cls.__init__ = wrapped_init
             cls._b200_wrapped = True
@@ -51,14 +57,18 @@ def uninstall() -> None:
     _saved.clear()
 
 
-def convert_frame_attention(aggregator) -> int:
-    """Turn the `attn` module of every frame block into a B200FrameAttention.  The module keeps its
-    parameters and attributes (qkv, q_norm, k_norm, proj, rope, num_heads, head_dim); only forward changes."""
+def convert_frame_attention(aggregator, patch_embed: bool = False) -> int:
+    """Turn the `attn` module of every frame block (and, with patch_embed, of every block of a ViT patch embed)
+    into a B200FrameAttention.  The module keeps its parameters and attributes (qkv, q_norm, k_norm, proj, rope,
+    num_heads, head_dim); only forward changes."""
     from .block import B200FrameAttention
+    blocks = list(getattr(aggregator, "frame_blocks", []))
+    if patch_embed:
+        blocks += [b for b in getattr(getattr(aggregator, "patch_embed", None), "blocks", []) if hasattr(b, "attn")]
     n = 0
-    for blk in getattr(aggregator, "frame_blocks", []):
+    for blk in blocks:
         attn = blk.attn
-        if attn.head_dim == 64 and not isinstance(attn, B200FrameAttention):
+        if getattr(attn, "head_dim", 0) == 64 and hasattr(attn, "qkv") and not isinstance(attn, B200FrameAttention):
             attn.__class__ = B200FrameAttention
             n += 1
     return n

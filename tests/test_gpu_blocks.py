@@ -129,3 +129,18 @@ def test_bf16_autocast_path():
         assert got.dtype == torch.bfloat16
         close(got, want.double().cpu().numpy(), f"bf16 frame {i}", max_abs=8e-2, cos=0.999)
     assert m1.build_visible_page_table(0) == m2.build_visible_page_table(0)
+
+
+def test_plain_attention_without_norm_and_rope():
+    """The DINOv2 patch-embed attention (vision_transformer.py:144-171 builds Block(attn_class=Attention) with
+    qk_norm off and no RoPE; 1 class + 4 register + 999 patch tokens): B200FrameAttention against fp32 SDPA."""
+    dim, H, N = 128, 2, 1004
+    fa = P.B200FrameAttention(dim, num_heads=H, qk_norm=False, rope=None).eval().to(DEV)
+    seeded.fill_module_(fa, 31)
+    x = torch.from_numpy(seeded.randn(77, 2, N, dim)).to(DEV)
+    with torch.no_grad():
+        y = fa(x)
+        qkv = fa.qkv(x).reshape(2, N, 3, H, 64).permute(2, 0, 3, 1, 4)
+        ref = torch.nn.functional.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2])
+        ref = fa.proj(ref.transpose(1, 2).reshape(2, N, dim))
+    close(y, ref.double().cpu().numpy(), "plain attention")
