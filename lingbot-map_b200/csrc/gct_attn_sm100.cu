@@ -719,7 +719,12 @@ void choose_attention_config(int n_q_tiles, int heads_x_batch, int total_blocks,
                              int* q_tiles_per_cta, int* splits) {
   // Cost model in units of "one KV block for one CTA": a CTA with two query tiles takes about as long
   // per block as one with a single tile takes for 0.6 blocks-worth of its pair; every CTA pays a fixed
-  // prologue/epilogue of about two blocks.  Pick the cheapest (tiles per CTA, splits).
+  // prologue/epilogue of about two blocks, and a split result needs the merge kernel afterwards (a launch
+  // of its own, about five blocks).  Pick the cheapest (tiles per CTA, splits).
+#ifndef GCT_MERGE_COST
+#define GCT_MERGE_COST 5.0
+#endif
+  constexpr double kMergeCost = GCT_MERGE_COST;
   double best = 1e300;
   int best_qt = 1, best_s = 1;
   for (int qt = 2; qt >= 1; --qt) {
@@ -730,7 +735,7 @@ void choose_attention_config(int n_q_tiles, int heads_x_batch, int total_blocks,
       const long long ctas = items * s;
       const long long waves = (ctas + num_sms - 1) / num_sms;
       const int blocks = (total_blocks + s - 1) / s;
-      const double cost = static_cast<double>(waves) * (blocks * per_block + 2.0) + (s > 1 ? 0.5 : 0.0);
+      const double cost = static_cast<double>(waves) * (blocks * per_block + 2.0) + (s > 1 ? kMergeCost : 0.0);
       if (cost < best - 1e-9) {
         best = cost;
         best_qt = qt;
