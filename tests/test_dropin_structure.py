@@ -66,3 +66,40 @@ def test_rebinding_builds_b200_blocks_in_reference_aggregator():
     finally:
         stream_mod.FlashInferBlock, cache_mod.FlashInferKVCacheManager, stream_mod.AggregatorStream.__init__ = saved
         stream_mod.AggregatorStream._b200_wrapped = False
+
+
+def test_custom_operators_are_registered_with_fake_implementations():
+    """torch.compile of the reference's frame blocks traces the kernels as opaque operators: shapes and dtypes come
+    from the fake implementations, no kernel runs."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    assert hasattr(torch.ops.gct_b200, "dense_attention") and hasattr(torch.ops.gct_b200, "prep_qkv")
+    with FakeTensorMode():
+        q = torch.empty(2, 100, 4, 64, dtype=torch.bfloat16)
+        o = torch.ops.gct_b200.dense_attention(q, q, q)
+        assert o.shape == (2, 100, 4, 64) and o.dtype == torch.bfloat16
+        a, b, c = torch.ops.gct_b200.prep_qkv(torch.empty(200, 768), 4, 100, None, None, None, None, None, 0)
+        assert a.shape == b.shape == c.shape == (200, 4, 64) and a.dtype == torch.bfloat16
+
+
+def test_cpu_tensors_are_rejected_not_computed():
+    q = torch.zeros(1, 4, 2, 64, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        P.ops.dense_attention(q, q, q)
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lingbot_map")), reason="reference checkout not present")
+def test_install_and_uninstall_restore_reference_names():
+    sys.path.insert(0, REF)
+    import lingbot_map.aggregator.stream as stream_mod
+    import lingbot_map.layers.flashinfer_cache as cache_mod
+    before = (stream_mod.FlashInferBlock, cache_mod.FlashInferKVCacheManager, stream_mod.AggregatorStream.__init__)
+    P.select.install(patch_embed_attention=True)
+    try:
+        assert stream_mod.FlashInferBlock is P.B200Block
+        agg = stream_mod.AggregatorStream(img_size=56, patch_size=14, embed_dim=1024, depth=1, num_heads=16,
+                                          patch_embed="conv", enable_3d_rope=True, max_frame_num=32)
+        assert isinstance(agg.frame_blocks[0].attn, P.B200FrameAttention)
+    finally:
+        P.select.uninstall()
+    assert (stream_mod.FlashInferBlock, cache_mod.FlashInferKVCacheManager,
+            stream_mod.AggregatorStream.__init__) == before
