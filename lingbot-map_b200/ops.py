@@ -38,9 +38,9 @@ def dense_attention(q: Tensor, k: Tensor, v: Tensor, out: Optional[Tensor] = Non
 
     q [B, Nq, H, 64], k/v [B, Nkv, H, 64] bf16 with arbitrary strides (head_dim contiguous, strides
     multiples of 8 elements) -> [B, Nq, H, 64] bf16 contiguous."""
-    if out is None:
-        return torch.ops.gct_b200.dense_attention(q, k, v)
-    return _dense_attention_impl(q, k, v, out)
+    if out is None and torch.compiler.is_compiling():
+        return torch.ops.gct_b200.dense_attention(q, k, v)      # one opaque node in the traced graph
+    return _dense_attention_impl(q, k, v, out)                  # eager: straight to the C ABI
 
 
 def _dense_attention_impl(q: Tensor, k: Tensor, v: Tensor, out: Optional[Tensor] = None) -> Tensor:
@@ -69,8 +69,10 @@ def prep_qkv(qkv: Tensor, heads: int, tokens_per_frame: int, q_norm_w, q_norm_b,
     """qkv Linear output [tokens, 3*H*64] -> (q, k, v) bf16 [tokens, H, 64]: LayerNorm(64) on q and k,
     RoPE from the per-token cos/sin table (indexed by token % tokens_per_frame), v cast only
     (lingbot_map/layers/attention.py:67-73)."""
-    return torch.ops.gct_b200.prep_qkv(qkv, heads, tokens_per_frame, q_norm_w, q_norm_b, k_norm_w, k_norm_b, rope_cs,
-                                       rope_mode)
+    if torch.compiler.is_compiling():
+        return torch.ops.gct_b200.prep_qkv(qkv, heads, tokens_per_frame, q_norm_w, q_norm_b, k_norm_w, k_norm_b, rope_cs,
+                                           rope_mode)
+    return _prep_qkv_impl(qkv, heads, tokens_per_frame, q_norm_w, q_norm_b, k_norm_w, k_norm_b, rope_cs, rope_mode)
 
 
 def _prep_qkv_impl(qkv: Tensor, heads: int, tokens_per_frame: int, q_norm_w, q_norm_b, k_norm_w, k_norm_b,

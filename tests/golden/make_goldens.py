@@ -331,7 +331,8 @@ def model_e2e_values():
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("LINGBOT_MAP_REFERENCE"), required="LINGBOT_MAP_REFERENCE" not in os.environ,
+                    help="checkout of the reference repository (or set LINGBOT_MAP_REFERENCE)")
     ap.add_argument("--only", default="", help="comma-separated fixture names (default: all)")
     args = ap.parse_args()
     _import_reference(args.reference)

@@ -13,7 +13,9 @@ import torch
 import lingbot_map_b200 as P
 
 G = os.path.join(os.path.dirname(__file__), "golden")
-REF = "/root/reference"
+# a checkout or an installed copy of the reference package: LINGBOT_MAP_REFERENCE, else baseline/_ref of this repository
+REF = os.environ.get("LINGBOT_MAP_REFERENCE",
+                     os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref"))
 
 
 def test_block_parameter_names_match_reference():
