@@ -365,3 +365,35 @@ def test_argument_errors_are_reported_not_trapped():
     with pytest.raises(AssertionError, match="expected 20 patch tokens"):
         m.append_frame(0, torch.zeros(25, 2, 64, device=DEV), torch.zeros(25, 2, 64, device=DEV))
     assert m.device_status() == 0
+
+
+def test_dense_attention_and_prologue_capture_into_a_cuda_graph():
+    """The launches of gct_attn_dense and gct_prep_qkv are plain stream work: after one warm-up call (which sizes the
+    per-device scratch) they capture into a CUDA graph and replay on new input values, as they do inside the
+    reference's torch.compile(mode="reduce-overhead") wrappers."""
+    import lingbot_map_b200 as P
+    from lingbot_map_b200 import ops
+    dev = "cuda:0"
+    H, N = 4, 300
+    g = torch.Generator(device=dev).manual_seed(3)
+    qkv = torch.randn(N, 3 * H * 64, generator=g, device=dev)
+    static_in = qkv.clone()
+
+    def step(x):
+        q, k, v = ops.prep_qkv(x, H, N, None, None, None, None, None, 0)
+        return ops.dense_attention(q.view(1, N, H, 64), k.view(1, N, H, 64), v.view(1, N, H, 64))
+
+    want0 = step(static_in).clone()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        static_out = step(static_in)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(static_out, want0)
+    qkv2 = torch.randn(N, 3 * H * 64, generator=g, device=dev)
+    static_in.copy_(qkv2)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(static_out, step(qkv2))
+    assert ops.device_status(dev) == 0
