@@ -112,6 +112,7 @@ def main(argv=None):
         e1.record()
         torch.cuda.synchronize()
         per_frame.append(e0.elapsed_time(e1))
+    in_order = [round(x, 2) for x in per_frame]
     per_frame.sort()
     med = per_frame[len(per_frame) // 2]
     mean = sum(per_frame) / len(per_frame)
@@ -120,7 +121,8 @@ def main(argv=None):
                                              if isinstance(v, (int, float, bool))},
                       "frames_timed": args.frames, "ms_per_frame_median": round(med, 3),
                       "ms_per_frame_mean": round(mean, 3), "frames_per_s_median": round(1000.0 / med, 2),
-                      "frames_per_s_mean": round(1000.0 / mean, 2), "prefill_s": round(fill_s, 1),
+                      "frames_per_s_mean": round(1000.0 / mean, 2), "ms_per_frame_max": round(per_frame[-1], 3), "ms_in_order": in_order,
+                      "prefill_s": round(fill_s, 1),
                       "image": f"{args.img_h}x{args.img_w}", "dtype": "bf16 autocast"}))
 
 
