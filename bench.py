@@ -123,6 +123,7 @@ class HotPath:
             for _ in range(n_cached):
                 self.mgr.append_frame_bookkeeping(b)
                 self.mgr.evict_frames(b, SCALE_FRAMES, WINDOW)
+        self.mgr.rescan_key_norms()             # the pages were filled directly: recompute the key-norm maxima
         C = HEADS * HEAD_DIM
         rn = lambda *s: torch.randn(*s, device=device, generator=g)
         self.qkv_frame = [rn(TPF, 3 * C).to(torch.bfloat16) for _ in range(DEPTH)]

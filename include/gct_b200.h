@@ -86,8 +86,20 @@ int gct_mgr_workspace_bytes(const gct_mgr_t* m, size_t* bytes_out);
  * k_dev/v_dev: [tokens_per_frame, H, 64] contiguous, dtype GCT_F32 or GCT_BF16. */
 int gct_mgr_append(gct_mgr_t* m, int block, const void* k_dev, int k_dtype, const void* v_dev, int v_dtype,
                    void* stream);
-/* Same bookkeeping without touching device memory (tests, dry runs, replicas that do not own a page). */
+/* Same bookkeeping without touching device memory (tests, dry runs, replicas that do not own a page).  The
+ * caller is then responsible for the page contents; bounded mode (below) is switched off for the block until
+ * gct_mgr_scan_keys is called. */
 int gct_mgr_append_bookkeeping(gct_mgr_t* m, int block);
+
+/* Bounded mode of the paged attention (no counterpart in the reference): the manager keeps, per block and head,
+ * the largest 2-norm of the K rows written through gct_mgr_append / gct_mgr_append_fused.  |q_row| times that
+ * maximum bounds every logit of the row, and while the bound is small (checked on the device for every call) it
+ * replaces the running row maximum of the online softmax, which removes the maximum and rescale work from the
+ * kernel; otherwise the exact kernel runs.  Results are the same softmax either way.
+ * gct_mgr_scan_keys recomputes the maxima of a block from its whole pool (after writing pages directly);
+ * gct_mgr_set_bounded_mode(m, 0) forces the exact kernel. */
+int gct_mgr_scan_keys(gct_mgr_t* m, int block, void* stream);
+int gct_mgr_set_bounded_mode(gct_mgr_t* m, int enable);
 
 /* Fused tail of FlashInferAttention.prepare_qkv (lingbot_map/layers/attention.py:413-426) and
  * append_frame: from the qkv Linear output [tokens, 3*H*64] apply LayerNorm(64) to q and k

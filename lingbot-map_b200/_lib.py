@@ -45,6 +45,8 @@ SIGNATURES = {
     "gct_mgr_workspace_bytes": (_i, [_vp, C.POINTER(_sz)]),
     "gct_mgr_append": (_i, [_vp, _i, _vp, _i, _vp, _i, _vp]),
     "gct_mgr_append_bookkeeping": (_i, [_vp, _i]),
+    "gct_mgr_scan_keys": (_i, [_vp, _i, _vp]),
+    "gct_mgr_set_bounded_mode": (_i, [_vp, _i]),
     "gct_mgr_append_fused": (_i, [_vp, _i, _vp, _i, _i64, _pf, _pf, _pf, _pf, _pf, _i, _vp, _vp]),
     "gct_mgr_evict": (_i, [_vp, _i, _i]),
     "gct_mgr_exec_deferred": (_i, [_vp, _i, _i]),

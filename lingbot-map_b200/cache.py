@@ -132,8 +132,23 @@ class B200KVCacheManager:
                                              v.data_ptr(), _dtype_code(v), _stream_ptr(self.device)))
 
     def append_frame_bookkeeping(self, block_idx: int) -> None:
-        """append_frame without device writes (dry runs; KV-sharded replicas that do not own the page)."""
+        """append_frame without device writes (dry runs; KV-sharded replicas that do not own the page).  Whoever
+        fills the pages directly calls rescan_key_norms() afterwards to re-enable the bounded attention mode."""
         self._check(self._lib.gct_mgr_append_bookkeeping(self._handle, block_idx))
+
+    def rescan_key_norms(self, block_idx: Optional[int] = None) -> None:
+        """Recompute the per-head maximum key norm of a block (all blocks by default) from its pool, after pages
+        were written without going through append_frame / append_frame_fused."""
+        self._require_device()
+        blocks = range(self.num_blocks) if block_idx is None else [block_idx]
+        with torch.cuda.device(self.device):
+            for b in blocks:
+                self._check(self._lib.gct_mgr_scan_keys(self._handle, b, _stream_ptr(self.device)))
+
+    def set_bounded_mode(self, enable: bool) -> None:
+        """Bounded mode (default on) lets the paged attention use |q|*max|k| as a fixed softmax reference when that
+        bound is small; off forces the kernel that tracks the running row maximum.  Same softmax either way."""
+        self._check(self._lib.gct_mgr_set_bounded_mode(self._handle, 1 if enable else 0))
 
     def append_frame_fused(self, block_idx: int, qkv: Tensor, q_norm_w, q_norm_b, k_norm_w, k_norm_b,
                            rope_cs: Optional[Tensor], rope_mode: int, q_out: Optional[Tensor] = None) -> Tensor:

@@ -226,6 +226,13 @@ struct KernelArgs {
   float* part_o;
   float* part_lse;
   int* status;
+  // Bounded mode (see gct_row_ref_kernel): row_ref[row] >= every scaled logit of the row, so it serves as a fixed
+  // softmax reference and the kernel needs neither row maxima nor rescaling.  *unsafe_epoch == epoch means that the
+  // bound of some row was too loose: the bounded kernel then returns at once and the exact kernel does the work;
+  // otherwise the exact kernel returns at once.  unsafe_epoch == nullptr: exact kernel only.
+  const float* row_ref;
+  const int* unsafe_epoch;
+  int epoch;
 };
 
 constexpr int kKStages = 4;
@@ -250,6 +257,14 @@ constexpr int kSumLag = GCT_SUM_LAG;
 #endif
 constexpr int kPvWaitAt = GCT_PV_WAIT_AT;    // pair (31..61) after which the sweep waits for the previous PV and stores P[0,64)
 constexpr int kMaxChains = GCT_MAX_CHAINS;
+#ifndef GCT_BOUNDED_OVERLAP
+#define GCT_BOUNDED_OVERLAP 1
+#endif
+#ifndef GCT_POLY_EVERY_BOUNDED
+#define GCT_POLY_EVERY_BOUNDED GCT_POLY_EVERY
+#endif
+constexpr int kPolyEveryBounded = GCT_POLY_EVERY_BOUNDED;    // share of polynomial exponentials in bounded mode
+constexpr bool kBoundedOverlap = GCT_BOUNDED_OVERLAP != 0;   // bounded mode: sweep the first half while the second loads
 // Register budget at two query tiles per CTA: 384 threads start with 168 registers each (64512 in total);
 // the control warpgroup shrinks to kControlRegs and the two softmax warpgroups grow to kSoftmaxRegs:
 // 128 * kControlRegs + 256 * kSoftmaxRegs <= 64512, both multiples of 8.
@@ -282,11 +297,15 @@ struct SmemLayout {
 template <int QT>
 constexpr int kThreads = (QT == 2) ? 384 : 192;
 
-template <int QT>
+template <int QT, bool kBounded>
 __global__ void __launch_bounds__(kThreads<QT>, 1)
 gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const KernelArgs a) {
   using L = SmemLayout<QT>;
+  if (a.unsafe_epoch != nullptr) {
+    const bool unsafe = *a.unsafe_epoch == a.epoch;
+    if (unsafe == kBounded) return;              // the other instantiation handles this launch
+  }
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -446,6 +465,11 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t p_addr = tmem_base + lane_addr + kPCol + t * 64;
     const float c = a.scale_log2;
     float m = -INFINITY, l = 0.f;                   // m: reference maximum (raw logit units)
+    float ref_fixed = 0.f;                          // bounded mode: upper bound of this row's scaled logits
+    if constexpr (kBounded) {
+      const int qr = (qg * QT + t) * kTileM + row;
+      ref_fixed = a.row_ref[(static_cast<size_t>(b) * a.n_q + (qr < a.n_q ? qr : 0)) * a.heads + h];
+    }
     bool ok = true;
     uint32_t s[128];
 
@@ -468,6 +492,7 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           for (int i = 0; i < 64; ++i)
             if (lo + i >= valid) s[lo + i] = 0xff800000u;   // -inf: exp2 gives 0
         }
+        if constexpr (kBounded) return 0.f;       // the reference is fixed: only the masking above is needed
         // kMaxChains independent chains of 3-input max, merged by a tree at the end
         float mxc[kMaxChains];
 #pragma unroll
@@ -514,21 +539,26 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_ld32(s_addr + 64, s2);
         tmem_ld32(s_addr + 96, s3);
         const float mlo = half_max(0);
-        tmem_wait_ld();
-        // the S tile is in registers: the tensor core may overwrite it with the next block
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_s_empty(t));
-        mx = fmaxf(mlo, half_max(64));
+        if constexpr (!(kBounded && kBoundedOverlap)) {
+          tmem_wait_ld();
+          // the S tile is in registers: the tensor core may overwrite it with the next block
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_s_empty(t));
+        }
+        if constexpr (kBounded && kBoundedOverlap) mx = mlo;   // the second half is masked after its load, in the sweep
+        else mx = fmaxf(mlo, half_max(64));
       }
       // move the reference maximum only when the row maximum outgrew it by more than 2^kRescaleThreshold;
       // until then exponentials stay below 2^8 and every sum remains exact enough in fp32
       float alpha = 1.f;
-      if ((mx - m) * c > kRescaleThreshold) {      // always true on the first block (m = -inf)
-        alpha = fast_exp2((m - mx) * c);           // exp2(-inf) = 0 on the first block
-        m = mx;
+      if constexpr (!kBounded) {
+        if ((mx - m) * c > kRescaleThreshold) {      // always true on the first block (m = -inf)
+          alpha = fast_exp2((m - mx) * c);           // exp2(-inf) = 0 on the first block
+          m = mx;
+        }
       }
-      const float mc = m * c;
+      const float mc = kBounded ? ref_fixed : m * c;
 
       // P (and O) of this tile are free once the PV product of the previous block has completed.  The wait
       // sits in the middle of the exponential sweep, right before the first store of P, so that the
@@ -537,7 +567,7 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (j > 0) {
           if (!mbar_wait(bar_pv_full(t), (j - 1) & 1, cta_abort, a.status)) return false;
           tc_fence_after();
-          if (__any_sync(0xffffffffu, alpha != 1.f)) {   // rare: rescale this warp's 32 rows of O in TMEM
+          if (!kBounded && __any_sync(0xffffffffu, alpha != 1.f)) {   // rare: rescale this warp's 32 rows of O in TMEM
             uint32_t ob[32];
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
@@ -563,7 +593,8 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         s[2 * q + 1] = __float_as_uint(x.y);
       };
       auto pair_exp = [&](int q) {
-        if (kPolyEvery > 0 && (q % (kPolyEvery > 0 ? kPolyEvery : 1)) == (kPolyEvery - 1)) {
+        constexpr int every = kBounded ? kPolyEveryBounded : kPolyEvery;
+        if (every > 0 && (q % (every > 0 ? every : 1)) == (every - 1)) {
           // every kPolyEvery-th pair is exponentiated on the FMA pipe: the special-function unit delivers only
           // 16 results per clock and SM, half of what the tensor core consumes at head_dim 64
           const float2 e = exp2_poly2(make_float2(__uint_as_float(s[2 * q]), __uint_as_float(s[2 * q + 1])));
@@ -583,6 +614,20 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int q = 0; q < kFfmaAhead; ++q) pair_ffma(q);
 #pragma unroll
       for (int q = 0; q < 64; ++q) {
+        if constexpr (kBounded && kBoundedOverlap) {
+          // bounded mode needs no row maximum: the second half of the S row arrives under the first half of the sweep
+          if (q == 32 - kFfmaAhead) {
+            tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_s_empty(t));
+            if (valid < 128) {
+#pragma unroll
+              for (int i = 64; i < 128; ++i)
+                if (i >= valid) s[i] = 0xff800000u;
+            }
+          }
+        }
         if (q + kFfmaAhead < 64) pair_ffma(q + kFfmaAhead);
         pair_exp(q);
         if (q >= kSumLag) {
@@ -641,7 +686,8 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
       }
-      if (qrow < a.n_q && !a.final_bf16) a.part_lse[prow] = (m * c + log2f(l)) * 0.6931471805599453f;
+      if (qrow < a.n_q && !a.final_bf16)
+        a.part_lse[prow] = ((kBounded ? ref_fixed : m * c) + log2f(l)) * 0.6931471805599453f;
     }
   }
 
@@ -689,6 +735,12 @@ int launch_attention(const AttnLaunch& a, cudaStream_t stream) {
   k.part_o = a.part_o;
   k.part_lse = a.part_lse;
   k.status = a.status;
+  k.row_ref = a.row_ref;
+  k.unsafe_epoch = a.unsafe_epoch;
+  k.epoch = a.epoch;
+  const bool bounded = a.unsafe_epoch != nullptr;
+  if (bounded && (a.row_ref == nullptr || a.q_tiles_per_cta != 2))
+    return fail(GCT_ERR_INVALID, "attention: bounded mode needs row references and two query tiles per CTA");
   if (a.splits < 1 || a.splits > k.total_blocks) return fail(GCT_ERR_INVALID, "attention: splits out of range");
   if (a.final_bf16 && (a.splits != 1 || a.out == nullptr)) return fail(GCT_ERR_INVALID, "attention: final output needs splits == 1");
   if (!a.final_bf16 && (a.part_o == nullptr || a.part_lse == nullptr))
@@ -699,17 +751,21 @@ int launch_attention(const AttnLaunch& a, cudaStream_t stream) {
   if (a.q_tiles_per_cta == 2) {
     static bool attr_set = false;
     if (!attr_set) {
-      GCT_CUDA_CHECK(cudaFuncSetAttribute(gct_attn_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      GCT_CUDA_CHECK(cudaFuncSetAttribute(gct_attn_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      GCT_CUDA_CHECK(cudaFuncSetAttribute(gct_attn_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       attr_set = true;
     }
-    gct_attn_kernel<2><<<static_cast<unsigned>(grid), kThreads<2>, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
+    // bounded mode: both instantiations are launched; each CTA of the one that does not apply returns at once
+    if (bounded)
+      gct_attn_kernel<2, true><<<static_cast<unsigned>(grid), kThreads<2>, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
+    gct_attn_kernel<2, false><<<static_cast<unsigned>(grid), kThreads<2>, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
   } else {
     static bool attr_set = false;
     if (!attr_set) {
-      GCT_CUDA_CHECK(cudaFuncSetAttribute(gct_attn_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      GCT_CUDA_CHECK(cudaFuncSetAttribute(gct_attn_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       attr_set = true;
     }
-    gct_attn_kernel<1><<<static_cast<unsigned>(grid), kThreads<1>, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
+    gct_attn_kernel<1, false><<<static_cast<unsigned>(grid), kThreads<1>, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
   }
   GCT_CUDA_CHECK(cudaGetLastError());
   return GCT_OK;

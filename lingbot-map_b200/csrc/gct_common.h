@@ -51,6 +51,11 @@ struct AttnLaunch {
   float* part_o = nullptr;           // [splits, batch, n_q, H, 64] normalised partial outputs
   float* part_lse = nullptr;         // [splits, batch, n_q, H] natural log-sum-exp
   int* status = nullptr;             // device status word
+  // bounded mode (two query tiles per CTA only): per-row upper bounds of the scaled logits from
+  // launch_row_ref, and the word it sets to `epoch` when some bound is too loose to be used
+  const float* row_ref = nullptr;    // [batch, n_q, H]
+  const int* unsafe_epoch = nullptr;
+  int epoch = 0;
 };
 int launch_attention(const AttnLaunch& a, cudaStream_t stream);
 int attention_smem_bytes(int q_tiles_per_cta);
@@ -86,9 +91,17 @@ struct PrepLaunch {
   int patch_page = -1;               // tokens >= num_special go to row (token - num_special) of this page
   int sp_page0 = -1, sp_off0 = 0, sp_n0 = 0, sp_page1 = -1;   // specials: first sp_n0 at sp_off0 of page0, rest at row 0.. of page1
   int* status = nullptr;
+  float* key_norm_max = nullptr;     // [H] running maximum of the 2-norms of the K rows written (paged destination)
 };
 int launch_prep(const PrepLaunch& p, cudaStream_t stream);
 
+// row_ref[row] = |q_row| * key_norm_max[head] * scale * log2(e) for the rows of q [rows/heads, heads, 64] bf16;
+// *unsafe_epoch = epoch when a reference exceeds `limit` (or is not finite).
+int launch_row_ref(const __nv_bfloat16* q, int64_t rows, int heads, const float* key_norm_max, float limit,
+                   float* row_ref, int* unsafe_epoch, int epoch, cudaStream_t stream);
+// key_norm_max[head] = max over all K rows of the pool [pages, 2, page_size, heads, 64] of their 2-norm
+int launch_scan_keys(const __nv_bfloat16* pool, int num_pages, int page_size, int heads, float* key_norm_max,
+                     cudaStream_t stream);
 int launch_cast_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream_t stream);
 // parts_stride / lse_stride: elements between consecutive groups (0 = densely packed).
 int launch_merge(const float* parts, const float* lse, int groups, int64_t rows /* n_q*H */, __nv_bfloat16* out_bf16,

@@ -183,6 +183,19 @@ __global__ void __launch_bounds__(256) gct_prep_kernel(const PrepLaunch p) {
       store8(k_row + dst, k);
       store8(v_row + dst, v);
     }
+    if (p.key_norm_max != nullptr) {
+      // running maximum of |k| per head (an upper bound: fp32 values, inflated for the bf16 rounding).  Positive
+      // floats order like their bit patterns; the plain read first keeps atomics rare once the maximum settles.
+      float sq = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sq += k.v[i] * k.v[i];
+      const float nrm = sqrtf(row_sum(sq)) * 1.004f;
+      if (active && part == 0) {
+        unsigned int* slot = reinterpret_cast<unsigned int*>(p.key_norm_max + hh);
+        if (!(nrm <= __uint_as_float(*reinterpret_cast<volatile unsigned int*>(slot))))   // also taken for NaN
+          atomicMax(slot, nrm == nrm ? __float_as_uint(nrm) : 0x7f800000u);
+      }
+    }
   }
 }
 
@@ -224,6 +237,49 @@ gct_merge_kernel(const float* __restrict__ parts, const float* __restrict__ lse,
   if (out_f32 != nullptr)
     *reinterpret_cast<float2*>(out_f32 + row * kHeadDim + 2 * lane) = make_float2(acc.x * inv, acc.y * inv);
   if (lse_out != nullptr && lane == 0) lse_out[row] = mx + logf(den);
+}
+
+// One warp per query row: reference = |q| * max|k| of the head * scale * log2(e) >= every scaled logit of the row
+// (Cauchy-Schwarz), usable as a fixed softmax reference while it stays below `limit`.
+__global__ void __launch_bounds__(256)
+gct_row_ref_kernel(const __nv_bfloat16* __restrict__ q, int64_t rows, int heads, const float* __restrict__ key_norm_max,
+                   float limit, float* __restrict__ row_ref, int* unsafe_epoch, int epoch) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (row >= rows) return;
+  const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(q + row * kHeadDim + 2 * lane);
+  const float2 f = __bfloat1622float2(v);
+  float sq = f.x * f.x + f.y * f.y;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+  if (lane == 0) {
+    const float ref = sqrtf(sq) * key_norm_max[row % heads] * (0.125f * 1.4426950408889634f);
+    row_ref[row] = ref;
+    if (!(ref <= limit)) atomicExch(unsafe_epoch, epoch);   // too loose, infinite or NaN
+  }
+}
+
+// One warp per K row of the pool.
+__global__ void __launch_bounds__(256)
+gct_scan_keys_kernel(const __nv_bfloat16* __restrict__ pool, int64_t total_rows, int page_size, int heads,
+                     float* key_norm_max) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t rows_per_page = static_cast<int64_t>(page_size) * heads;
+  for (int64_t r = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; r < total_rows; r += warps) {
+    const int64_t page = r / rows_per_page, in_page = r - page * rows_per_page;
+    const __nv_bfloat16* src = pool + (page * 2 * rows_per_page + in_page) * kHeadDim;   // K region of the page
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + 2 * lane));
+    float sq = f.x * f.x + f.y * f.y;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    if (lane == 0) {
+      const float nrm = sqrtf(sq);
+      unsigned int* slot = reinterpret_cast<unsigned int*>(key_norm_max + in_page % heads);
+      if (!(nrm <= __uint_as_float(*reinterpret_cast<volatile unsigned int*>(slot))))
+        atomicMax(slot, nrm == nrm ? __float_as_uint(nrm) : 0x7f800000u);
+    }
+  }
 }
 
 // cs[token][m] = (cos, sin) of the m-th complex frequency; fp64 angles as the reference's table
@@ -314,6 +370,27 @@ int launch_merge(const float* parts, const float* lse, int groups, int64_t rows,
   const int blocks = static_cast<int>((rows * 32 + 255) / 256);
   gct_merge_kernel<<<blocks, 256, 0, stream>>>(parts, lse, groups, rows, parts_stride, lse_stride, out_bf16, out_f32,
                                                lse_out);
+  GCT_CUDA_CHECK(cudaGetLastError());
+  return GCT_OK;
+}
+
+int launch_row_ref(const __nv_bfloat16* q, int64_t rows, int heads, const float* key_norm_max, float limit,
+                   float* row_ref, int* unsafe_epoch, int epoch, cudaStream_t stream) {
+  if (q == nullptr || key_norm_max == nullptr || row_ref == nullptr || unsafe_epoch == nullptr || rows <= 0 || heads <= 0)
+    return fail(GCT_ERR_INVALID, "row_ref: bad argument");
+  const int blocks = static_cast<int>((rows * 32 + 255) / 256);
+  gct_row_ref_kernel<<<blocks, 256, 0, stream>>>(q, rows, heads, key_norm_max, limit, row_ref, unsafe_epoch, epoch);
+  GCT_CUDA_CHECK(cudaGetLastError());
+  return GCT_OK;
+}
+
+int launch_scan_keys(const __nv_bfloat16* pool, int num_pages, int page_size, int heads, float* key_norm_max,
+                     cudaStream_t stream) {
+  if (pool == nullptr || key_norm_max == nullptr || num_pages <= 0 || page_size <= 0 || heads <= 0)
+    return fail(GCT_ERR_INVALID, "scan_keys: bad argument");
+  GCT_CUDA_CHECK(cudaMemsetAsync(key_norm_max, 0, static_cast<size_t>(heads) * sizeof(float), stream));
+  const int64_t total_rows = static_cast<int64_t>(num_pages) * page_size * heads;
+  gct_scan_keys_kernel<<<148 * 8, 256, 0, stream>>>(pool, total_rows, page_size, heads, key_norm_max);
   GCT_CUDA_CHECK(cudaGetLastError());
   return GCT_OK;
 }

@@ -95,6 +95,14 @@ struct gct_mgr {
   float* part_o = nullptr;
   float* part_lse = nullptr;
   int max_splits = 0;
+  // bounded softmax reference: running max of |k| per (block, head) on the device, kept by every K write that goes
+  // through the manager; per-row references and the "bound too loose" word of the current attention call
+  float* key_norm_max = nullptr;     // [num_blocks, H] inside the workspace header (null: does not fit)
+  float* row_ref = nullptr;          // [tokens_per_frame, H]
+  int* unsafe_epoch = nullptr;
+  int epoch = 0;
+  bool bounded_enabled = true;
+  std::vector<char> key_norm_valid, key_norm_clear;
   // plan
   bool planned = false;
   int plan_pages = 0, plan_last_len = 0;
@@ -111,6 +119,9 @@ struct gct_mgr {
 
 static constexpr size_t kWsHeader = 4096;      // status word
 static constexpr int kMaxSplitsCap = 32;
+// Largest |q| * max|k| * scale * log2(e) for which the bound may stand in for the row maximum: all exponents stay
+// in [-2 * limit, 0], far inside the fp32 / bf16 exponent range.
+static constexpr float kBoundedLimit = 40.0f;
 
 static void reset_block(const gct_mgr* m, BlockState& b) {
   b.scale_pages.clear();
@@ -128,14 +139,17 @@ static void reset_block(const gct_mgr* m, BlockState& b) {
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct WsLayout {
-  size_t table_off, qstage_off, parto_off, partlse_off, total_min, per_split;
+  size_t table_off, qstage_off, rowref_off, parto_off, partlse_off, total_min, per_split;
 };
+static constexpr size_t kWsEpochOff = 64;        // "bound too loose" word of the bounded mode
+static constexpr size_t kWsKeyNormOff = 256;     // key_norm_max[num_blocks][H] up to the end of the header
 static WsLayout ws_layout(const gct_mgr* m) {
   WsLayout w;
   const size_t rows = static_cast<size_t>(m->cfg.tokens_per_frame) * m->cfg.num_heads;
   w.table_off = kWsHeader;
   w.qstage_off = align_up(w.table_off + static_cast<size_t>(m->geo.max_num_pages) * 4, 256);
-  w.parto_off = align_up(w.qstage_off + rows * kHeadDim * 2, 256);
+  w.rowref_off = align_up(w.qstage_off + rows * kHeadDim * 2, 256);
+  w.parto_off = align_up(w.rowref_off + rows * 4, 256);
   w.per_split = rows * kHeadDim * 4 + rows * 4;
   w.partlse_off = 0;
   w.total_min = w.parto_off + 2 * w.per_split + 256;
@@ -258,6 +272,14 @@ int gct_mgr_bind(gct_mgr_t* m, void* const* pools_dev, void* workspace_dev, size
   m->part_o = reinterpret_cast<float*>(m->ws + w.parto_off);
   m->part_lse = reinterpret_cast<float*>(m->ws + w.parto_off + static_cast<size_t>(m->max_splits) * rows * kHeadDim * 4);
   GCT_CUDA_CHECK(cudaMemset(m->ws, 0, kWsHeader));
+  m->row_ref = reinterpret_cast<float*>(m->ws + w.rowref_off);
+  m->unsafe_epoch = reinterpret_cast<int*>(m->ws + kWsEpochOff);
+  m->epoch = 0;
+  const size_t kn_bytes = static_cast<size_t>(m->cfg.num_blocks) * H * sizeof(float);
+  m->key_norm_max = kWsKeyNormOff + kn_bytes <= kWsHeader ? reinterpret_cast<float*>(m->ws + kWsKeyNormOff) : nullptr;
+  // nothing is visible yet and the header was just zeroed: a maximum of 0 is exact
+  m->key_norm_valid.assign(m->cfg.num_blocks, 1);
+  m->key_norm_clear.assign(m->cfg.num_blocks, 0);
   m->bound = true;
   m->planned = false;
   m->tmq_ptr = nullptr;
@@ -321,7 +343,12 @@ static int append_bookkeeping(gct_mgr* m, int block, AppendPlan* plan) {
   return GCT_OK;
 }
 
-int gct_mgr_append_bookkeeping(gct_mgr_t* m, int block) { return append_bookkeeping(m, block, nullptr); }
+int gct_mgr_append_bookkeeping(gct_mgr_t* m, int block) {
+  const int rc = append_bookkeeping(m, block, nullptr);
+  // the caller writes the pool itself: the key-norm maximum no longer covers what is visible (gct_mgr_scan_keys)
+  if (rc == GCT_OK && m->bound && block >= 0 && block < static_cast<int>(m->key_norm_valid.size())) m->key_norm_valid[block] = 0;
+  return rc;
+}
 
 static int check_bound(const gct_mgr* m) {
   if (m == nullptr) return fail(GCT_ERR_INVALID, "null manager");
@@ -331,6 +358,19 @@ static int check_bound(const gct_mgr* m) {
 }  // extern "C"
 static int check_bound_fwd(const gct_mgr* m) { return check_bound(m); }
 extern "C" {
+
+// Key-norm tracking of an append on `stream`: clear a maximum left over from before a reset, then let the kernel
+// raise it.
+static int track_key_norms(gct_mgr* m, int block, PrepLaunch* p, cudaStream_t stream) {
+  if (m->key_norm_max == nullptr) return GCT_OK;
+  float* slot = m->key_norm_max + static_cast<size_t>(block) * m->cfg.num_heads;
+  if (m->key_norm_clear[block]) {
+    GCT_CUDA_CHECK(cudaMemsetAsync(slot, 0, static_cast<size_t>(m->cfg.num_heads) * sizeof(float), stream));
+    m->key_norm_clear[block] = 0;
+  }
+  p->key_norm_max = slot;
+  return GCT_OK;
+}
 
 static void fill_paged_dst(const gct_mgr* m, int block, const AppendPlan& pl, PrepLaunch* p) {
   p->pool = m->pools[block];
@@ -365,6 +405,8 @@ int gct_mgr_append(gct_mgr_t* m, int block, const void* k_dev, int k_dtype, cons
   p.src_dtype_v = v_dtype;
   p.src_token_stride = static_cast<int64_t>(m->cfg.num_heads) * kHeadDim;
   p.src_head_stride = kHeadDim;
+  rc = track_key_norms(m, block, &p, static_cast<cudaStream_t>(stream));
+  if (rc != GCT_OK) return rc;
   m->launches += 1;
   return launch_prep(p, static_cast<cudaStream_t>(stream));
 }
@@ -399,6 +441,8 @@ int gct_mgr_append_fused(gct_mgr_t* m, int block, const void* qkv_dev, int qkv_d
   p.rope_cs = rope_cs_dev;
   p.rope_mode = rope_mode;
   p.q_out = static_cast<__nv_bfloat16*>(q_out_dev);
+  rc = track_key_norms(m, block, &p, static_cast<cudaStream_t>(stream));
+  if (rc != GCT_OK) return rc;
   m->launches += 1;
   return launch_prep(p, static_cast<cudaStream_t>(stream));
 }
@@ -459,10 +503,33 @@ int gct_mgr_rollback(gct_mgr_t* m, int block) {
   return GCT_OK;
 }
 
+int gct_mgr_scan_keys(gct_mgr_t* m, int block, void* stream) {
+  int rc = check_bound(m);
+  if (rc != GCT_OK) return rc;
+  if (block < 0 || block >= m->cfg.num_blocks) return fail(GCT_ERR_INVALID, "gct_mgr_scan_keys: block index out of range");
+  if (m->key_norm_max == nullptr) return GCT_OK;       // bounded mode unavailable for this geometry
+  rc = launch_scan_keys(m->pools[block], m->geo.max_num_pages, m->geo.page_size, m->cfg.num_heads,
+                        m->key_norm_max + static_cast<size_t>(block) * m->cfg.num_heads, static_cast<cudaStream_t>(stream));
+  if (rc != GCT_OK) return rc;
+  m->key_norm_valid[block] = 1;
+  m->key_norm_clear[block] = 0;
+  m->launches += 1;
+  return GCT_OK;
+}
+
+int gct_mgr_set_bounded_mode(gct_mgr_t* m, int enable) {
+  if (m == nullptr) return fail(GCT_ERR_INVALID, "null manager");
+  m->bounded_enabled = enable != 0;
+  return GCT_OK;
+}
+
 int gct_mgr_reset(gct_mgr_t* m) {
   if (m == nullptr) return fail(GCT_ERR_INVALID, "null manager");
   for (auto& b : m->blocks) reset_block(m, b);
   m->planned = false;
+  // nothing is visible any more: the key-norm maxima restart from zero at the next append
+  for (auto& f : m->key_norm_clear) f = 1;
+  for (auto& f : m->key_norm_valid) f = 1;
   return GCT_OK;
 }
 
@@ -593,6 +660,21 @@ static int run_paged(gct_mgr* m, int block, const void* q_dev, int q_dtype, int 
   if (rc != GCT_OK) return rc;
   choose_attention_config((n_q + kTileM - 1) / kTileM, H, total_blocks, sms, m->max_splits, &a.q_tiles_per_cta, &a.splits);
   const int64_t rows = static_cast<int64_t>(n_q) * H;
+  // Bounded mode: every key of this block's cache went through the manager, so |q_row| * max|k| bounds the row's
+  // logits; while that bound stays small it replaces the running row maximum (decided on the device, per call).
+  if (m->bounded_enabled && m->key_norm_max != nullptr && m->key_norm_valid[block] && a.q_tiles_per_cta == 2) {
+    if (++m->epoch <= 0) {
+      m->epoch = 1;
+      GCT_CUDA_CHECK(cudaMemsetAsync(m->unsafe_epoch, 0, sizeof(int), stream));
+    }
+    rc = launch_row_ref(q, rows, H, m->key_norm_max + static_cast<size_t>(block) * H, kBoundedLimit, m->row_ref,
+                        m->unsafe_epoch, m->epoch, stream);
+    if (rc != GCT_OK) return rc;
+    a.row_ref = m->row_ref;
+    a.unsafe_epoch = m->unsafe_epoch;
+    a.epoch = m->epoch;
+    m->launches += 2;      // the reference kernel and the second attention instantiation
+  }
   if (a.splits == 1 && out_bf16 != nullptr && lse_dev == nullptr) {
     a.final_bf16 = true;
     a.out = out_bf16;

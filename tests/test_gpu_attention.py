@@ -397,3 +397,65 @@ def test_dense_attention_and_prologue_capture_into_a_cuda_graph():
     torch.cuda.synchronize()
     assert torch.equal(static_out, step(qkv2))
     assert ops.device_status(dev) == 0
+
+
+def _cache_with_frames(scale, n_frames, tpf=262, H=2, seed=11, kscale=1.0):
+    import lingbot_map_b200 as P
+    dev = "cuda:0"
+    m = P.B200KVCacheManager(1, 2 + 4 + 16, tpf, H, 64, device=dev, scale_frames=2, sliding_window=4, max_total_frames=64)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    for _ in range(n_frames):
+        k = torch.randn(tpf, H, 64, generator=g, device=dev) * kscale
+        v = torch.randn(tpf, H, 64, generator=g, device=dev)
+        m.append_frame(0, k, v)
+        m.evict_frames(0, 2, 4)
+    q = (torch.randn(tpf, H, 64, generator=g, device=dev) * scale).to(torch.bfloat16)
+    return m, q
+
+
+@pytest.mark.parametrize("qscale,kscale,tag", [(1.0, 1.0, "bound small: fixed reference"),
+                                               (12.0, 12.0, "bound too loose: exact kernel takes over")])
+def test_bounded_and_exact_modes_agree_with_the_oracle(qscale, kscale, tag):
+    """Bounded mode (|q| * max|k| as a fixed softmax reference, chosen on the device per call) and the exact mode
+    compute the same softmax: both within the attention tolerance of the oracle, and of each other."""
+    from oracle import gct_oracle as O
+    m, q = _cache_with_frames(qscale, 9, kscale=kscale)
+    kk, vv = m._gather_kv(0)
+    out_b = m.compute_attention(0, q).float().cpu().numpy()
+    m.set_bounded_mode(False)
+    out_e = m.compute_attention(0, q).float().cpu().numpy()
+    assert m.device_status() == 0
+    ref, _ = O.attention(q.float().cpu().numpy().astype(np.float64), kk.float().cpu().numpy().astype(np.float64),
+                         vv.float().cpu().numpy().astype(np.float64))
+    for name, got in (("bounded", out_b), ("exact", out_e)):
+        d = float(np.abs(got - ref).max())
+        c = float((got.ravel() @ ref.ravel()) / (np.linalg.norm(got) * np.linalg.norm(ref)))
+        assert d <= 2e-2 and c >= 0.9999, f"{tag}, {name}: max_abs={d:.3e} cosine={c:.6f}"
+    assert float(np.abs(out_b - out_e).max()) <= 1e-2
+
+
+def test_key_norm_tracking_survives_reset_and_direct_pool_writes():
+    """The key-norm maximum restarts after reset(); bookkeeping-only appends switch bounded mode off until
+    rescan_key_norms(), so pages written directly never meet a stale bound."""
+    from oracle import gct_oracle as O
+    m, q = _cache_with_frames(1.0, 7, kscale=30.0)          # huge keys first
+    m.reset()
+    g = torch.Generator(device="cuda:0").manual_seed(5)
+    for _ in range(3):
+        m.append_frame(0, torch.randn(262, 2, 64, generator=g, device="cuda:0"),
+                       torch.randn(262, 2, 64, generator=g, device="cuda:0"))
+        m.evict_frames(0, 2, 4)
+    def check():
+        kk, vv = m._gather_kv(0)
+        got = m.compute_attention(0, q).float().cpu().numpy()
+        ref, _ = O.attention(q.float().cpu().numpy().astype(np.float64), kk.float().cpu().numpy().astype(np.float64),
+                             vv.float().cpu().numpy().astype(np.float64))
+        assert float(np.abs(got - ref).max()) <= 2e-2
+    check()
+    m.append_frame_bookkeeping(0)                           # page content: whatever the pool holds
+    m.evict_frames(0, 2, 4)
+    m.kv_caches[0][:, 0] *= 50.0                            # direct write: keys far beyond the tracked maximum
+    check()                                                 # exact kernel (bounded mode is off for the block)
+    m.rescan_key_norms(0)
+    check()                                                 # bound recomputed: too loose -> exact kernel again
+    assert m.device_status() == 0
