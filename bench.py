@@ -176,6 +176,8 @@ def run_gpu(args):
     extra = args.steps + args.warmup + 8 + args.e2e_steps
     hp = HotPath(dev, args.frames_cached, extra, seed=100 + (0 if kvsplit else rank),
                  shard=(rank, world) if kvsplit else None)
+    if args.exact_softmax:
+        hp.mgr.set_bounded_mode(False)
     m = hp.mgr
 
     def barrier():
@@ -409,6 +411,8 @@ def main():
     ap.add_argument("--frames-cached", type=int, default=10000)
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exact-softmax", action="store_true",
+                    help="force the attention instantiation that tracks the running row maximum (bounded mode off)")
     ap.add_argument("--layers", type=int, default=24,
                     help="aggregator depth; the metric is defined at 24, smaller values are for profiler captures")
     args = ap.parse_args()

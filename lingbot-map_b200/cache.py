@@ -6,6 +6,7 @@ C ABI (bit-exact page tables and eviction decisions); K/V pages are written by a
 attention over the visible pages runs on the tcgen05 kernel.  There is no CPU compute path.
 """
 import ctypes as C
+import os
 from typing import List, Optional
 
 import torch
@@ -94,6 +95,8 @@ class B200KVCacheManager:
                 _lib.check(self._lib.gct_mgr_bind(self._handle, pools, self.workspace_buffer.data_ptr(),
                                                   self.workspace_buffer.numel()))
             self._bound = True
+            if os.environ.get("LINGBOT_B200_BOUNDED_SOFTMAX", "1") == "0":
+                self.set_bounded_mode(False)
 
     def __del__(self):
         h = getattr(self, "_handle", None)
