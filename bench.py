@@ -318,7 +318,7 @@ def run_gpu(args):
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the paged attention kernel.  Captured with
 # ncu on a small case (kv = 73,146 tokens: 340.3 MB, see profiles/gct_attn_kernel_paged_kv73k.md) and
 # scaled to the benchmark's KV length by the number of key tokens, which the traffic is proportional to.
-NCU_DRAM_BYTES_SMALL_CASE = 347.36e6
+NCU_DRAM_BYTES_SMALL_CASE = 339.64e6
 NCU_SMALL_CASE_KV = 73146
 
 

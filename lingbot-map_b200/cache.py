@@ -148,6 +148,16 @@ class B200KVCacheManager:
             for b in blocks:
                 self._check(self._lib.gct_mgr_scan_keys(self._handle, b, _stream_ptr(self.device)))
 
+    @property
+    def key_norm_max(self) -> Tensor:
+        """[num_blocks, H] fp32 view of the per-head maxima of the key 2-norms kept in the workspace header (an upper
+        bound over everything written since the last reset; meaningful only while the manager wrote the pages)."""
+        self._require_device()
+        n = self.num_blocks * self.num_heads
+        if 256 + 4 * n > 4096:
+            raise RuntimeError("bounded mode is unavailable for this geometry (num_blocks * num_heads > 960)")
+        return self.workspace_buffer[256:256 + 4 * n].view(torch.float32).view(self.num_blocks, self.num_heads)
+
     def set_bounded_mode(self, enable: bool) -> None:
         """Bounded mode (default on) lets the paged attention use |q|*max|k| as a fixed softmax reference when that
         bound is small; off forces the kernel that tracks the running row maximum.  Same softmax either way."""

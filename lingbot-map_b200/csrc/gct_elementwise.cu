@@ -259,25 +259,42 @@ gct_row_ref_kernel(const __nv_bfloat16* __restrict__ q, int64_t rows, int heads,
   }
 }
 
-// One warp per K row of the pool.
+// Eight lanes per K row of the pool (16 bytes each), four rows per warp and load, four loads in flight per lane.
 __global__ void __launch_bounds__(256)
 gct_scan_keys_kernel(const __nv_bfloat16* __restrict__ pool, int64_t total_rows, int page_size, int heads,
                      float* key_norm_max) {
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, part = lane & 7, sub = lane >> 3;
   const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int64_t rows_per_page = static_cast<int64_t>(page_size) * heads;
-  for (int64_t r = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; r < total_rows; r += warps) {
-    const int64_t page = r / rows_per_page, in_page = r - page * rows_per_page;
-    const __nv_bfloat16* src = pool + (page * 2 * rows_per_page + in_page) * kHeadDim;   // K region of the page
-    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + 2 * lane));
-    float sq = f.x * f.x + f.y * f.y;
+  constexpr int kUnroll = 4;
+  for (int64_t base = ((static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5) * (4 * kUnroll);
+       base < total_rows; base += warps * (4 * kUnroll)) {
+    uint4 v[kUnroll];
+    int head[kUnroll];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-    if (lane == 0) {
-      const float nrm = sqrtf(sq);
-      unsigned int* slot = reinterpret_cast<unsigned int*>(key_norm_max + in_page % heads);
-      if (!(nrm <= __uint_as_float(*reinterpret_cast<volatile unsigned int*>(slot))))
-        atomicMax(slot, nrm == nrm ? __float_as_uint(nrm) : 0x7f800000u);
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t r = base + 4 * u + sub;
+      const int64_t rr = r < total_rows ? r : total_rows - 1;          // tail: repeat the last row
+      const int64_t page = rr / rows_per_page, in_page = rr - page * rows_per_page;
+      head[u] = static_cast<int>(in_page % heads);
+      v[u] = *reinterpret_cast<const uint4*>(pool + (page * 2 * rows_per_page + in_page) * kHeadDim + 8 * part);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+      float sq = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+        sq += f.x * f.x + f.y * f.y;
+      }
+      sq = row_sum(sq);
+      if (part == 0) {
+        const float nrm = sqrtf(sq);
+        unsigned int* slot = reinterpret_cast<unsigned int*>(key_norm_max + head[u]);
+        if (!(nrm <= __uint_as_float(*reinterpret_cast<volatile unsigned int*>(slot))))
+          atomicMax(slot, nrm == nrm ? __float_as_uint(nrm) : 0x7f800000u);
+      }
     }
   }
 }

@@ -459,3 +459,22 @@ def test_key_norm_tracking_survives_reset_and_direct_pool_writes():
     m.rescan_key_norms(0)
     check()                                                 # bound recomputed: too loose -> exact kernel again
     assert m.device_status() == 0
+
+
+def test_key_norm_maxima_track_appends_and_rescan():
+    """The tracked maximum bounds the true key norms from above within the 0.4 % rounding allowance, restarts after
+    reset, and rescan_key_norms() reproduces the maximum over the whole pool."""
+    m, _ = _cache_with_frames(1.0, 9, kscale=3.0)
+    def pool_max():
+        k = m.kv_caches[0][:, 0].float()                      # [pages, page_size, H, 64]
+        return k.norm(dim=-1).amax(dim=(0, 1))
+    true = pool_max()                                         # untouched pages are zero
+    got = m.key_norm_max[0].clone()
+    assert torch.all(got >= true * 0.999) and torch.all(got <= true * 1.01), (got, true)
+    m.reset()
+    g = torch.Generator(device="cuda:0").manual_seed(1)
+    m.append_frame(0, torch.randn(262, 2, 64, generator=g, device="cuda:0") * 0.1,
+                   torch.randn(262, 2, 64, generator=g, device="cuda:0"))
+    assert torch.all(m.key_norm_max[0] < 2.0)                 # restarted: the old, larger keys no longer count
+    m.rescan_key_norms(0)
+    assert torch.allclose(m.key_norm_max[0], pool_max(), rtol=1e-3)   # whole pool, stale pages included
