@@ -77,19 +77,28 @@ class ClockSampler:
 
         def pump():
             for line in self.proc.stdout:
-                self.rows.append([x.strip() for x in line.split(",")])
+                self.rows.append((time.perf_counter(), [x.strip() for x in line.split(",")]))
         self.thread = threading.Thread(target=pump, daemon=True)
         self.thread.start()
+
+    def mark_begin(self):
+        """Start of the timed region: only samples from here on (to a little past its end) are reported."""
+        self.t_begin = time.perf_counter()
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        t_end = time.perf_counter()
         time.sleep(0.25)
         self.proc.terminate()
         self.thread.join(timeout=2)
         sm, mx, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        t_begin = getattr(self, "t_begin", 0.0)
+        inside = [r for t, r in self.rows if t_begin <= t <= t_end + 0.25]
+        if not inside and self.rows:          # region shorter than the sampling period: the sample nearest to it
+            inside = [min(self.rows, key=lambda tr: abs(tr[0] - t_end))[1]]
+        for r in inside:
             if len(r) < 7:
                 continue
             try:
@@ -185,6 +194,10 @@ def run_gpu(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # the sampler runs from before the warm-up (nvidia-smi takes a while to start on a multi-GPU host); only its
+    # samples from the timed region are reported
+    sampler = ClockSampler(dev)
+    sampler.start()
     for _ in range(args.warmup):
         hp.step()
     barrier()
@@ -192,8 +205,7 @@ def run_gpu(args):
     # ---- timed region: device-resident inputs ----
     m.kernel_timing(args.steps * DEPTH)
     m.kernel_time()
-    sampler = ClockSampler(dev)
-    sampler.start()
+    sampler.mark_begin()
     launches0 = hp.launches
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
