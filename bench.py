@@ -90,6 +90,10 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         t_end = time.perf_counter()
         time.sleep(0.25)
+        for _ in range(30):                    # a slow nvidia-smi start-up: wait for its first row rather than report none
+            if self.rows:
+                break
+            time.sleep(0.1)
         self.proc.terminate()
         self.thread.join(timeout=2)
         sm, mx, reasons = [], None, set()
@@ -183,6 +187,10 @@ def run_gpu(args):
         dist.init_process_group("nccl", device_id=dev)
     kvsplit = args.mode == "kvsplit" and world > 1
     extra = args.steps + args.warmup + 8 + args.e2e_steps
+    # the sampler runs from before the set-up (nvidia-smi takes a while to start on a multi-GPU host); only its
+    # samples from the timed region are reported
+    sampler = ClockSampler(dev)
+    sampler.start()
     hp = HotPath(dev, args.frames_cached, extra, seed=100 + (0 if kvsplit else rank),
                  shard=(rank, world) if kvsplit else None)
     if args.exact_softmax:
@@ -194,10 +202,6 @@ def run_gpu(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # the sampler runs from before the warm-up (nvidia-smi takes a while to start on a multi-GPU host); only its
-    # samples from the timed region are reported
-    sampler = ClockSampler(dev)
-    sampler.start()
     for _ in range(args.warmup):
         hp.step()
     barrier()
