@@ -478,3 +478,32 @@ def test_key_norm_maxima_track_appends_and_rescan():
     assert torch.all(m.key_norm_max[0] < 2.0)                 # restarted: the old, larger keys no longer count
     m.rescan_key_norms(0)
     assert torch.allclose(m.key_norm_max[0], pool_max(), rtol=1e-3)   # whole pool, stale pages included
+
+
+@pytest.mark.parametrize("n_past,kv_expected", [(1000, 23085), (10000, 77085)])
+@pytest.mark.parametrize("dist", ["randn_over_8", "unit_variance"])
+def test_single_layer_microbench_shapes(n_past, kv_expected, dist):
+    """The single-layer configuration of the headline benchmark: one frame of 1005 query tokens x 16 heads x 64 over
+    1 anchor frame + 16 window frames (full tokens) + 6 memory tokens for each of the past frames, built through the
+    manager (scale 1, window 16) so that the page layout is the real one.  Values ~ N(0,1)/8 from seed 1 (logits are
+    then almost uniform and the cosine is the binding check), and a unit-variance distribution with a peaked softmax."""
+    tpf, H = 1005, 16
+    m = P.B200KVCacheManager(1, 1 + 16 + 16, tpf, H, 64, device=DEV, scale_frames=1, sliding_window=16,
+                             max_total_frames=n_past + 64)
+    gen = torch.Generator(device=DEV).manual_seed(1)
+    scale = 0.125 if dist == "randn_over_8" else 1.0
+    kf = (torch.randn(8, tpf, H, 64, device=DEV, generator=gen) * scale).to(torch.bfloat16)   # 8 distinct frames, cycled
+    vf = (torch.randn(8, tpf, H, 64, device=DEV, generator=gen) * scale).to(torch.bfloat16)
+    for t in range(17 + n_past):
+        m.append_frame(0, kf[t % 8], vf[t % 8])
+        m.evict_frames(0, 1, 16)
+    q = (torch.randn(tpf, H, 64, device=DEV, generator=gen) * scale).to(torch.bfloat16)
+    out = m.compute_attention(0, q)
+    kk, vv = m._gather_kv(0)
+    assert kk.shape[0] == kv_expected
+    rows = [0, 5, 6, 127, 128, 640, 1004]
+    for h in (0, 9, 15):
+        want, _ = O.attention(q[rows][:, h:h + 1].float().cpu().numpy(), kk[:, h:h + 1].float().cpu().numpy(),
+                              vv[:, h:h + 1].float().cpu().numpy())
+        assert_close(out[rows][:, h:h + 1], want, f"{dist} n_past={n_past} head {h}")
+    assert m.device_status() == 0
