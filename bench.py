@@ -418,6 +418,7 @@ def run_reference(args):
 
 
 def main():
+    global DEPTH, SCALE_FRAMES, WINDOW
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -436,7 +437,6 @@ def main():
     ap.add_argument("--layers", type=int, default=24,
                     help="aggregator depth; the metric is defined at 24, smaller values are for profiler captures")
     args = ap.parse_args()
-    global DEPTH, SCALE_FRAMES, WINDOW
     DEPTH = args.layers
     SCALE_FRAMES, WINDOW = args.scale_frames, args.window
     if args.impl == "reference":
