@@ -105,3 +105,14 @@ def test_install_and_uninstall_restore_reference_names():
         P.select.uninstall()
     assert (stream_mod.FlashInferBlock, cache_mod.FlashInferKVCacheManager,
             stream_mod.AggregatorStream.__init__) == before
+
+
+def test_entry_scripts_compile_and_parse_their_arguments():
+    """bench.py and __graft_entry__.py byte-compile, and bench.py builds its argument parser (no GPU needed)."""
+    import py_compile
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for name in ("bench.py", "__graft_entry__.py"):
+        py_compile.compile(os.path.join(root, name), doraise=True)
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--help"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "--exact-softmax" in r.stdout and "--scale-frames" in r.stdout, r.stderr[-500:]
