@@ -309,13 +309,17 @@ def run_gpu(args):
                                    f"page 999, scale {SCALE_FRAMES} + window {WINDOW}, keyframe_interval 1",
                        "parallelism": ("kv-pages sharded over %d GPUs, NCCL all-gather + LSE merge" % world) if kvsplit
                        else ("%d independent stream(s), one per GPU" % world),
-                       "l2": f"inputs larger than L2 (each layer streams {kv_now * 4096 / 1e6:.0f} MB of K/V)",
+                       "l2": (f"inputs larger than L2 (each layer streams {kv_now * 4096 / 1e6:.0f} MB of K/V)"
+                              if kv_now * 4096 * DEPTH > 126e6 else
+                              f"K/V of all layers ({kv_now * 4096 * DEPTH / 1e6:.0f} MB) fit in L2: not a metric configuration"),
                        "clock_samples": clocks.get("samples")},
             "clocks": {k: clocks.get(k) for k in ("sm_mhz", "sm_max_mhz", "reasons")},
             "e2e": {"value": e2e_fps, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": args.e2e_steps},
             "gpu_launches": gpu_launches,
-            "roofline": {"bound": "tensor", "kernel": "gct_attn_kernel<2> (paged global attention)",
+            "roofline": {"bound": "tensor", "kernel": "gct_attn_kernel<2> (paged global attention, %s)" %
+                                   ("running row maximum" if args.exact_softmax else
+                                    "bounded softmax reference; both instantiations of a launch timed together"),
                          "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": (achieved / peaks["bf16_tflops"]) if achieved else None,
                          "peak_source": peaks["which"], "kernel_us": kern_s * 1e6, "launches_timed": attn_launches,
