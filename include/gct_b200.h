@@ -96,6 +96,8 @@ int gct_mgr_append_bookkeeping(gct_mgr_t* m, int block);
  * maximum bounds every logit of the row, and while the bound is small (checked on the device for every call) it
  * replaces the running row maximum of the online softmax, which removes the maximum and rescale work from the
  * kernel; otherwise the exact kernel runs.  Results are the same softmax either way.
+ * The maxima are floats [num_blocks][H] at byte offset 256 of the bound workspace (the mode is unavailable when they
+ * do not fit into its 4096-byte header, i.e. num_blocks * H > 960).
  * gct_mgr_scan_keys recomputes the maxima of a block from its whole pool (after writing pages directly);
  * gct_mgr_set_bounded_mode(m, 0) forces the exact kernel. */
 int gct_mgr_scan_keys(gct_mgr_t* m, int block, void* stream);
