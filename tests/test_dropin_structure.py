@@ -116,3 +116,28 @@ def test_entry_scripts_compile_and_parse_their_arguments():
         py_compile.compile(os.path.join(root, name), doraise=True)
     r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--help"], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "--exact-softmax" in r.stdout and "--scale-frames" in r.stdout, r.stderr[-500:]
+
+
+def test_clock_sampler_reports_samples_of_the_timed_region_only():
+    """bench.py's clock sampler against a stand-in for nvidia-smi: rows before mark_begin() are dropped, throttle
+    reasons of the kept rows are reported, and a region shorter than the sampling period still gets the nearest row."""
+    import importlib.util
+    import time
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    fake = ("import time,sys\n"
+            "rows=['1000, 1965, 300, Not Active, Not Active, Not Active, Not Active']*3+"
+            "['1900, 1965, 900, Not Active, Not Active, Not Active, Active']*50\n"
+            "for r in rows:\n    print(r, flush=True); time.sleep(0.05)\n")
+    s = bench.ClockSampler.__new__(bench.ClockSampler)
+    s.rows, s.proc, s.thread = [], None, None
+    s.cmd = [sys.executable, "-c", fake]
+    s.start()
+    time.sleep(0.4)                      # the three 1000 MHz rows fall before the timed region
+    s.mark_begin()
+    time.sleep(0.5)
+    got = s.stop()
+    assert got["sm_mhz"] == 1900.0 and got["sm_max_mhz"] == 1965.0 and got["reasons"] == ["sw_power_cap"], got
+    assert got["samples"] >= 3
