@@ -7,14 +7,26 @@ tokens + 6 memory tokens of every past frame = 131,928 visible KV tokens):
     frame block  : q/k LayerNorm + 2-D RoPE + bf16 cast  ->  dense attention 1005 x 1005
     global block : fused q/k LayerNorm + 3-D RoPE + bf16 K/V page append -> eviction -> paged attention
                    over the visible page table (split-KV + log-sum-exp merge)
-The qkv/proj Linear layers, MLPs, DINOv2 and the heads are outside the measured path.
+The qkv/proj Linear layers, MLPs, DINOv2 and the heads are outside the measured path (`whole_model` in the
+output line times the complete model behind the reference's interface, with either backend).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--mode streams|kvsplit]
+                    [--streams-per-gpu S]
 
 Prints ONE JSON line.  N > 1 is launched with torch.distributed.run, one rank per GPU:
-`streams` (default) runs one independent stream per GPU (weak scaling, no data-path collective);
-`kvsplit` shards one stream's visible pages over the GPUs and merges partial outputs with NCCL.
-`--impl reference` times the CPU port of the reference's SDPA streaming path on the host cores.
+`streams` (default) runs independent streams, S per GPU (weak scaling, no data-path collective), and adds a
+`kvsplit` sub-record: ONE stream whose visible pages are sharded over the GPUs (strong scaling), checked against
+the single-pass result before it is timed.  `--mode kvsplit` makes that the headline of the line instead.
+`--impl reference` times the reference's SDPA streaming path on the host cores.
+
+At N = 1 the line also carries, measured after and outside the timed regions:
+  cpu_baseline      the reference's CPU path on a bounded sample;
+  flashinfer_layer  the reference's own FlashInferKVCacheManager.compute_attention (plan once, run() timed) on a
+                    cache with the same page table and contents as this backend's, kv = 131,928, same GPU;
+  parity_at_headline  this backend's output for that layer against a float64 softmax over all rows of two heads
+                    and against FlashInfer's bf16 output on every element;
+  whole_model       frames/s of the whole GCTStream model at the 10k-frame cache with this backend and with the
+                    reference's FlashInfer backend (bench_model.py, one subprocess each).
 """
 import argparse
 import json
@@ -35,6 +47,7 @@ PPH, PPW, NSPECIAL = 27, 37, 6
 SCALE_FRAMES, WINDOW = 8, 64
 METRIC = "streaming frames/s @518x378 bf16 (steady state, 10k-frame KV); attn % of TC peak"
 UNIT = "frames/s"
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
 
 
 def visible_kv(n_cached):
@@ -46,8 +59,9 @@ def load_peaks():
     if os.path.exists(p):
         with open(p) as f:
             d = json.load(f)
-        return {"bf16_tflops": d["bf16_tflops_sustained"], "hbm_gbs": d["hbm_gbs"], "which": "measured (sustained)"}
-    return {"bf16_tflops": 1400.0, "hbm_gbs": 6650.0, "which": "fallback"}
+        return {"bf16_tflops": d["bf16_tflops_sustained"], "bf16_tflops_burst": d.get("bf16_tflops"),
+                "hbm_gbs": d["hbm_gbs"], "which": "measured (sustained)"}
+    return {"bf16_tflops": 1400.0, "bf16_tflops_burst": 1590.0, "hbm_gbs": 6650.0, "which": "fallback"}
 
 
 # ----------------------------------------------------------------------------- clocks
@@ -85,10 +99,13 @@ class ClockSampler:
         """Start of the timed region: only samples from here on (to a little past its end) are reported."""
         self.t_begin = time.perf_counter()
 
+    def mark_end(self):
+        self.t_end = time.perf_counter()
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
-        t_end = time.perf_counter()
+        t_end = getattr(self, "t_end", time.perf_counter())
         time.sleep(0.25)
         for _ in range(30):                    # a slow nvidia-smi start-up: wait for its first row rather than report none
             if self.rows:
@@ -115,6 +132,34 @@ class ClockSampler:
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
                 "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- host placement
+def bind_to_gpu_numa_node(device_index):
+    """Pin this process (and so the pinned host buffers it touches first) to the CPUs of the GPU's NUMA node.
+    Best effort: returns {"numa_node": n or None, "cpus": count} for the output line."""
+    info = {"numa_node": None, "cpus": len(os.sched_getaffinity(0))}
+    try:
+        bus = torch.cuda.get_device_properties(device_index).pci_bus_id
+        dom = torch.cuda.get_device_properties(device_index).pci_domain_id
+        dev = torch.cuda.get_device_properties(device_index).pci_device_id
+        path = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node"
+        with open(path) as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return info
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            info = {"numa_node": node, "cpus": len(cpus)}
+    except Exception:
+        pass
+    return info
 
 
 # ----------------------------------------------------------------------------- workload (GPU arm)
@@ -147,6 +192,7 @@ class HotPath:
         self.frame_index = n_cached
         self.outs = [None] * (2 * DEPTH)
         self.launches = 0
+        self.keep_q = None                      # set to a list to keep the global layers' q of the last step
 
     def step(self, qkv_frame=None, qkv_global=None, before_layer=None, after_layer=None):
         P, lib, m = self.P, self.lib, self.mgr
@@ -162,16 +208,184 @@ class HotPath:
             self.outs[2 * b] = P.ops.dense_attention(q[None], k[None], v[None])
             qg = m.append_frame_fused(b, qkv_global[b], *self.norm[2 * b + 1], self.cs3d, lib.ROPE_3D)
             m.evict_frames(b, SCALE_FRAMES, WINDOW)
+            if self.keep_q is not None:
+                self.keep_q.append(qg)
             if self.shard is None:
                 self.outs[2 * b + 1] = m.compute_attention(b, qg)
                 self.launches += 5          # prep, dense attention, fused append, paged attention, merge
             else:
                 from lingbot_map_b200 import distributed as D
                 self.outs[2 * b + 1] = D.sharded_attention(m, b, qg, *self.shard)
-                self.launches += 6          # ... + the cross-rank merge
+                self.launches += 5          # prep, dense attention, fused append, paged attention, exchange+merge
             if after_layer is not None:
                 after_layer(b)
         self.frame_index += 1
+
+
+def _cos64(a, b):
+    a, b = a.double().flatten(), b.double().flatten()
+    return float((a @ b) / (a.norm() * b.norm() + 1e-300))
+
+
+def timed_steps(step_fn, n, barrier, dev, world):
+    """n calls of step_fn between a barrier + synchronize on both sides; CUDA-event ms, max over ranks."""
+    import torch.distributed as dist
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(n):
+        step_fn()
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    local_ms = float(ms.item())
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item()), local_ms
+
+
+def measure(hps, args, dev, rank, world, barrier, sampler, kvsplit):
+    """The three timed regions for a list of streams on this GPU (one entry when kvsplit): device-resident inputs,
+    a second pass over the same steps with the attention kernel bracketed by events, and the end-to-end pass."""
+    import torch.distributed as dist
+    m0 = hps[0].mgr
+
+    def step_all():
+        for hp in hps:
+            hp.step()
+
+    for _ in range(args.warmup):
+        step_all()
+    barrier()
+    for hp in hps:
+        assert hp.mgr.device_status() == 0
+    # ---- timed region: device-resident inputs, no instrumentation ----
+    if sampler is not None:
+        sampler.mark_begin()
+    launches0 = sum(hp.launches for hp in hps)
+    t_wall = time.perf_counter()
+    total_ms, _ = timed_steps(step_all, args.steps, barrier, dev, world)
+    wall_s = time.perf_counter() - t_wall
+    if sampler is not None:
+        sampler.mark_end()
+    gpu_launches = sum(hp.launches for hp in hps) - launches0
+    # ---- second pass: the paged attention kernel alone, one CUDA-event pair per launch ----
+    ksteps = max(1, min(args.steps, args.kernel_steps))
+    m0.kernel_timing(ksteps * DEPTH)
+    m0.kernel_time()
+    for _ in range(ksteps):
+        hps[0].step()
+    attn_ms, attn_launches = m0.kernel_time()
+    m0.kernel_timing(0)
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    t0.record()
+    for _ in range(ksteps):
+        hps[0].step()
+    t1.record()
+    torch.cuda.synchronize()
+    one_stream_step_ms = t0.elapsed_time(t1) / ksteps
+    for hp in hps:
+        assert hp.mgr.device_status() == 0 and hp.P.ops.device_status(dev) == 0
+
+    # ---- end to end: host buffers in, host buffers out, copies inside the timed region ----
+    C3 = 3 * HEADS * HEAD_DIM
+    e2e = []
+    for hp in hps:
+        st = {"hp": hp}
+        st["h_in_f"] = [t.cpu().pin_memory() for t in hp.qkv_frame]
+        st["h_in_g"] = [t.cpu().pin_memory() for t in hp.qkv_global]
+        st["h_out"] = [torch.empty(TPF, HEADS, HEAD_DIM, dtype=torch.bfloat16).pin_memory() for _ in range(2 * DEPTH)]
+        st["d_in_f"] = [torch.empty(TPF, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)]
+        st["d_in_g"] = [torch.empty(TPF, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)]
+        e2e.append(st)
+    # Copies run on their own stream, one layer ahead of / behind the compute stream: the inputs of layer b
+    # are uploaded while layer b-1 computes, and the outputs of layer b are downloaded while layer b+1
+    # computes.  Events order every buffer hand-over in both directions.
+    copy_stream = torch.cuda.Stream(device=dev)
+    main_stream = torch.cuda.current_stream(dev)
+
+    def make_e2e_step(st):
+        hp = st["hp"]
+        ev_in = [torch.cuda.Event() for _ in range(DEPTH)]       # inputs of layer b are on the device
+        ev_free = [torch.cuda.Event() for _ in range(DEPTH)]     # layer b no longer reads its input buffers
+        ev_out = [torch.cuda.Event() for _ in range(DEPTH)]      # outputs of layer b are computed
+        for e in ev_free:
+            e.record(main_stream)
+
+        def upload(b):
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(ev_free[b])
+                st["d_in_f"][b].copy_(st["h_in_f"][b], non_blocking=True)
+                st["d_in_g"][b].copy_(st["h_in_g"][b], non_blocking=True)
+                ev_in[b].record(copy_stream)
+
+        def before_layer(b):
+            if b == 0:
+                upload(0)
+            if b + 1 < DEPTH:
+                upload(b + 1)
+            main_stream.wait_event(ev_in[b])
+
+        def after_layer(b):
+            ev_free[b].record(main_stream)
+            ev_out[b].record(main_stream)
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(ev_out[b])
+                for i in (2 * b, 2 * b + 1):
+                    hp.outs[i].record_stream(copy_stream)
+                    st["h_out"][i].copy_(hp.outs[i].view(TPF, HEADS, HEAD_DIM), non_blocking=True)
+
+        def e2e_step():
+            hp.step(st["d_in_f"], st["d_in_g"], before_layer, after_layer)
+            main_stream.wait_stream(copy_stream)                 # the step ends when its results are on the host
+        return e2e_step
+
+    e2e_steps = [make_e2e_step(st) for st in e2e]
+
+    def e2e_all():
+        for f in e2e_steps:
+            f()
+
+    e2e_all()
+    e2e_ms, e2e_local = timed_steps(e2e_all, args.e2e_steps, barrier, dev, world)
+    per_rank = [e2e_local]
+    if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, e2e_local)
+        per_rank = gathered
+    streams = 1 if kvsplit else world * len(hps)
+    return {
+        "total_ms": total_ms, "wall_s": wall_s, "gpu_launches": gpu_launches, "attn_ms": attn_ms,
+        "attn_launches": attn_launches, "one_stream_step_ms": one_stream_step_ms, "streams": streams,
+        "value": streams * args.steps / (total_ms / 1e3),
+        "e2e_value": streams * args.e2e_steps / (e2e_ms / 1e3),
+        "e2e_per_rank_fps": [len(hps) * args.e2e_steps / (x / 1e3) for x in per_rank],
+        "h2d": 2 * DEPTH * TPF * C3 * 2, "d2h": 2 * DEPTH * TPF * HEADS * HEAD_DIM * 2,
+    }
+
+
+def kvsplit_parity(hp, rank, dev):
+    """One frame of the KV-sharded stream; every global layer's merged output is compared on rank 0 with the
+    single-pass attention of the same layer over the whole page list (every rank holds the whole replicated pool)."""
+    m = hp.mgr
+    hp.keep_q = []
+    hp.step()
+    qs, hp.keep_q = hp.keep_q, None
+    torch.cuda.synchronize()
+    worst_abs, worst_cos = 0.0, 1.0
+    if rank == 0:
+        for b in range(DEPTH):
+            m.plan()                                            # the whole visible list
+            full = m.compute_attention.__func__(m, b, qs[b]) if b else m.compute_attention(0, qs[b])
+            got = hp.outs[2 * b + 1].view(TPF, HEADS, HEAD_DIM)
+            worst_abs = max(worst_abs, float((got.float() - full.float()).abs().max()))
+            worst_cos = min(worst_cos, _cos64(got, full))
+        m._shard_plan = None                                     # the next sharded call plans its slice again
+    ok = worst_abs <= 1e-2 and worst_cos >= 0.99999
+    return {"max_abs": worst_abs, "cosine": worst_cos, "layers": DEPTH, "ok": bool(ok),
+            "bound": "max_abs <= 1e-2, cosine >= 0.99999 against the single-pass output on rank 0"}
 
 
 def run_gpu(args):
@@ -182,153 +396,112 @@ def run_gpu(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch N>1 with torch.distributed.run")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    placement = bind_to_gpu_numa_node(local)
     import torch.distributed as dist
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    kvsplit = args.mode == "kvsplit" and world > 1
-    extra = args.steps + args.warmup + 8 + args.e2e_steps
+    headline_kvsplit = args.mode == "kvsplit" and world > 1
+    extra = 2 * args.steps + 2 * args.warmup + 3 * args.kernel_steps + 16 + 2 * args.e2e_steps
     # the sampler runs from before the set-up (nvidia-smi takes a while to start on a multi-GPU host); only its
     # samples from the timed region are reported
     sampler = ClockSampler(dev)
     sampler.start()
-    hp = HotPath(dev, args.frames_cached, extra, seed=100 + (0 if kvsplit else rank),
-                 shard=(rank, world) if kvsplit else None)
-    if args.exact_softmax:
-        hp.mgr.set_bounded_mode(False)
-    m = hp.mgr
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        hp.step()
-    barrier()
-    assert m.device_status() == 0
-    # ---- timed region: device-resident inputs ----
-    m.kernel_timing(args.steps * DEPTH)
-    m.kernel_time()
-    sampler.mark_begin()
-    launches0 = hp.launches
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        hp.step()
-    e1.record()
-    barrier()
-    ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    def build(kvsplit, n_streams):
+        hps = []
+        for s in range(n_streams):
+            seed = 100 + (0 if kvsplit else rank * n_streams + s)
+            hp = HotPath(dev, args.frames_cached, extra, seed=seed, shard=(rank, world) if kvsplit else None)
+            if args.exact_softmax:
+                hp.mgr.set_bounded_mode(False)
+            hps.append(hp)
+        return hps
+
+    hps = build(headline_kvsplit, 1 if headline_kvsplit else args.streams_per_gpu)
+    parity = kvsplit_parity(hps[0], rank, dev) if headline_kvsplit else None
+    res = measure(hps, args, dev, rank, world, barrier, sampler, headline_kvsplit)
     clocks = sampler.stop()
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    total_ms = float(ms.item())
-    attn_ms, attn_launches = m.kernel_time()
-    m.kernel_timing(0)
-    gpu_launches = hp.launches - launches0
-    assert m.device_status() == 0 and hp.P.ops.device_status(dev) == 0
-    n_cached_now = m.num_frames
+    n_cached_now = hps[0].mgr.num_frames
     kv_now = visible_kv(n_cached_now)
 
-    # ---- end to end: host buffers in, host buffers out, copies inside the timed region ----
-    C3 = 3 * HEADS * HEAD_DIM
-    h_in_f = [t.cpu().pin_memory() for t in hp.qkv_frame]
-    h_in_g = [t.cpu().pin_memory() for t in hp.qkv_global]
-    h_out = [torch.empty(TPF, HEADS, HEAD_DIM, dtype=torch.bfloat16).pin_memory() for _ in range(2 * DEPTH)]
-    d_in_f = [torch.empty(TPF, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)]
-    d_in_g = [torch.empty(TPF, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)]
-
-    # Copies run on their own stream, one layer ahead of / behind the compute stream: the inputs of layer b
-    # are uploaded while layer b-1 computes, and the outputs of layer b are downloaded while layer b+1
-    # computes.  Events order every buffer hand-over in both directions.
-    copy_stream = torch.cuda.Stream(device=dev)
-    main_stream = torch.cuda.current_stream(dev)
-    ev_in = [torch.cuda.Event() for _ in range(DEPTH)]       # inputs of layer b are on the device
-    ev_free = [torch.cuda.Event() for _ in range(DEPTH)]     # layer b no longer reads its input buffers
-    ev_out = [torch.cuda.Event() for _ in range(DEPTH)]      # outputs of layer b are computed
-    for e in ev_free:
-        e.record(main_stream)
-
-    def upload(b):
-        with torch.cuda.stream(copy_stream):
-            copy_stream.wait_event(ev_free[b])
-            d_in_f[b].copy_(h_in_f[b], non_blocking=True)
-            d_in_g[b].copy_(h_in_g[b], non_blocking=True)
-            ev_in[b].record(copy_stream)
-
-    def before_layer(b):
-        if b == 0:
-            upload(0)
-        if b + 1 < DEPTH:
-            upload(b + 1)
-        main_stream.wait_event(ev_in[b])
-
-    def after_layer(b):
-        ev_free[b].record(main_stream)
-        ev_out[b].record(main_stream)
-        with torch.cuda.stream(copy_stream):
-            copy_stream.wait_event(ev_out[b])
-            for i in (2 * b, 2 * b + 1):
-                hp.outs[i].record_stream(copy_stream)
-                h_out[i].copy_(hp.outs[i].view(TPF, HEADS, HEAD_DIM), non_blocking=True)
-
-    def e2e_step():
-        hp.step(d_in_f, d_in_g, before_layer, after_layer)
-        main_stream.wait_stream(copy_stream)                 # the step ends when its results are on the host
-
-    e2e_step()
-    barrier()
-    t0 = torch.cuda.Event(enable_timing=True)
-    t1 = torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(args.e2e_steps):
-        e2e_step()
-    t1.record()
-    barrier()
-    e2e_ms = torch.tensor([t0.elapsed_time(t1)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
-    streams = 1 if kvsplit else world
-    e2e_fps = streams * args.e2e_steps / (float(e2e_ms.item()) / 1e3)
-    h2d = 2 * DEPTH * TPF * C3 * 2
-    d2h = 2 * DEPTH * TPF * HEADS * HEAD_DIM * 2
+    sub = None
+    if world > 1 and not headline_kvsplit and not args.no_kvsplit:
+        # strong-scaling sub-record: one stream, visible pages sharded over all ranks
+        del hps
+        torch.cuda.empty_cache()
+        sub_args = argparse.Namespace(**vars(args))
+        sub_args.steps, sub_args.warmup, sub_args.e2e_steps = min(args.steps, 40), 3, min(args.e2e_steps, 3)
+        khps = build(True, 1)
+        kpar = kvsplit_parity(khps[0], rank, dev)
+        kres = measure(khps, sub_args, dev, rank, world, barrier, None, True)
+        sub = {"value": kres["value"], "unit": UNIT, "scaling": "strong", "steps": sub_args.steps,
+               "ms_per_step": kres["total_ms"] / sub_args.steps, "e2e": kres["e2e_value"], "parity": kpar,
+               "workload": "one stream, visible KV pages sharded over %d GPUs, peer exchange + LSE merge per layer" % world}
+        del khps
 
     if rank == 0:
         peaks = load_peaks()
         # algorithmic FLOPs of one launch of the paged attention kernel; a KV shard holds 1/world of the keys
-        flops = 4.0 * TPF * kv_now * HEAD_DIM * HEADS / (world if kvsplit else 1)
-        kern_s = attn_ms / max(attn_launches, 1) / 1e3
-        achieved = flops / kern_s / 1e12 if attn_launches else None
+        flops = 4.0 * TPF * kv_now * HEAD_DIM * HEADS / (world if headline_kvsplit else 1)
+        kern_s = res["attn_ms"] / max(res["attn_launches"], 1) / 1e3
+        achieved = flops / kern_s / 1e12 if res["attn_launches"] else None
+        sm = clocks.get("sm_mhz")
         line = {
-            "metric": METRIC, "value": streams * args.steps / (total_ms / 1e3), "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
-            "higher_is_better": True, "scaling": "strong" if kvsplit else "weak", "vs_baseline": None,
+            "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["total_ms"] / args.steps,
+            "higher_is_better": True, "scaling": "strong" if headline_kvsplit else "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"GCT hot path, {DEPTH} layers x (frame attention 1005x1005 + fused K/V append + "
                                    f"paged global attention), 518x378, {n_cached_now} cached frames, kv={kv_now} tokens, "
                                    f"page 999, scale {SCALE_FRAMES} + window {WINDOW}, keyframe_interval 1",
-                       "parallelism": ("kv-pages sharded over %d GPUs, NCCL all-gather + LSE merge" % world) if kvsplit
-                       else ("%d independent stream(s), one per GPU" % world),
+                       "parallelism": ("kv-pages sharded over %d GPUs, peer exchange + LSE merge" % world) if headline_kvsplit
+                       else ("%d independent stream(s), %d per GPU" % (res["streams"], args.streams_per_gpu)),
                        "l2": (f"inputs larger than L2 (each layer streams {kv_now * 4096 / 1e6:.0f} MB of K/V)"
                               if kv_now * 4096 * DEPTH > 126e6 else
                               f"K/V of all layers ({kv_now * 4096 * DEPTH / 1e6:.0f} MB) fit in L2: not a metric configuration"),
-                       "clock_samples": clocks.get("samples")},
+                       "clock_samples": clocks.get("samples"), "timed_region_s": res["wall_s"],
+                       "host_placement": placement},
             "clocks": {k: clocks.get(k) for k in ("sm_mhz", "sm_max_mhz", "reasons")},
-            "e2e": {"value": e2e_fps, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": args.e2e_steps},
-            "gpu_launches": gpu_launches,
+            "e2e": {"value": res["e2e_value"], "unit": UNIT, "h2d_bytes_per_step": res["h2d"],
+                    "d2h_bytes_per_step": res["d2h"], "steps": args.e2e_steps, "per_rank": res["e2e_per_rank_fps"]},
+            "gpu_launches": res["gpu_launches"],
             "roofline": {"bound": "tensor", "kernel": "gct_attn_kernel<2> (paged global attention, %s)" %
                                    ("running row maximum" if args.exact_softmax else
-                                    "bounded softmax reference; both instantiations of a launch timed together"),
+                                    "softmax reference folded into the S product"),
                          "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": (achieved / peaks["bf16_tflops"]) if achieved else None,
-                         "peak_source": peaks["which"], "kernel_us": kern_s * 1e6, "launches_timed": attn_launches,
-                         "flops_per_launch": flops, "attn_share_of_step": attn_ms / total_ms,
-                         "traffic": NCU_DRAM_BYTES_SMALL_CASE * kv_now / NCU_SMALL_CASE_KV / (world if kvsplit else 1),
+                         "frac_of_burst_peak": (achieved / peaks["bf16_tflops_burst"])
+                         if achieved and peaks.get("bf16_tflops_burst") else None,
+                         "peak_source": peaks["which"], "kernel_us": kern_s * 1e6,
+                         "kernel_us_x_sm_mhz": (kern_s * 1e6 * sm) if sm else None,
+                         "launches_timed": res["attn_launches"],
+                         "timed_in": "a second pass over the same steps, one CUDA-event pair per launch",
+                         "flops_per_launch": flops,
+                         "attn_share_of_step": (res["attn_ms"] / max(res["attn_launches"], 1) * DEPTH) / res["one_stream_step_ms"],
+                         "traffic": NCU_DRAM_BYTES_SMALL_CASE * kv_now / NCU_SMALL_CASE_KV / (world if headline_kvsplit else 1),
                          "traffic_source": "ncu small case scaled by KV tokens"},
         }
+        if parity is not None:
+            line["kvsplit_parity"] = parity
+        if sub is not None:
+            line["kvsplit"] = sub
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(max_seconds=25.0)
+    if world == 1 and rank == 0:
+        del hps
+        torch.cuda.empty_cache()
+        if not args.no_flashinfer:
+            rec = headline_layer_record(dev)
+            line["flashinfer_layer"] = rec["flashinfer_layer"]
+            line["parity_at_headline"] = rec["parity_at_headline"]
+        if not args.no_whole_model:
+            line["whole_model"] = whole_model_record(args)
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -342,58 +515,226 @@ NCU_DRAM_BYTES_SMALL_CASE = 339.64e6
 NCU_SMALL_CASE_KV = 73146
 
 
+# ----------------------------------------------------------------------------- same-box FlashInfer layer + parity
+def headline_layer_record(dev, n_cached=10000, repeats=30):
+    """One global layer at the headline geometry, built twice with identical contents: this backend's manager and the
+    reference's own FlashInferKVCacheManager (imported from baseline/_ref).  Times both (plan once, then run), and
+    checks this backend's output against a float64 softmax (all 1005 rows of two heads) and against FlashInfer."""
+    import lingbot_map_b200 as P
+    out = {"flashinfer_layer": None, "parity_at_headline": None}
+    g = torch.Generator(device=dev).manual_seed(7)
+    kf = torch.randn(8, TPF, HEADS, HEAD_DIM, device=dev, generator=g).to(torch.bfloat16)     # 8 frames, cycled
+    vf = torch.randn(8, TPF, HEADS, HEAD_DIM, device=dev, generator=g).to(torch.bfloat16)
+    q = torch.randn(TPF, HEADS, HEAD_DIM, device=dev, generator=g).to(torch.bfloat16)
+    m = P.B200KVCacheManager(1, SCALE_FRAMES + WINDOW + 16, TPF, HEADS, HEAD_DIM, device=dev,
+                             scale_frames=SCALE_FRAMES, sliding_window=WINDOW, max_total_frames=n_cached + 100)
+    for t in range(n_cached):
+        m.append_frame(0, kf[t % 8], vf[t % 8])
+        m.evict_frames(0, SCALE_FRAMES, WINDOW)
+    kv = visible_kv(n_cached)
+
+    def time_us(fn):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(repeats):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / repeats * 1e3
+
+    m.plan()
+    h = m._handle
+    from lingbot_map_b200 import _lib
+    ours = torch.empty(TPF, HEADS, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+    s = torch.cuda.current_stream(dev).cuda_stream
+    run_ours = lambda: _lib.check(m._lib.gct_mgr_attention(h, 0, q.data_ptr(), _lib.BF16, TPF, ours.data_ptr(), None, s))
+    b200_us = time_us(run_ours)
+    assert m.device_status() == 0
+    # float64 softmax on the same bf16 inputs, all rows of two heads (on the device, outside every timed region)
+    kk, vv = m._gather_kv(0)
+    assert kk.shape[0] == kv
+    worst_abs, worst_cos = 0.0, 1.0
+    for hd in (0, 11):
+        sc = (q[:, hd].double() @ kk[:, hd].double().T) * 0.125
+        want = torch.softmax(sc, dim=-1) @ vv[:, hd].double()
+        del sc
+        worst_abs = max(worst_abs, float((ours[:, hd].double() - want).abs().max()))
+        worst_cos = min(worst_cos, _cos64(ours[:, hd], want))
+    par = {"kv": kv, "vs_float64_softmax": {"rows": TPF, "heads": [0, 11], "max_abs": worst_abs, "cosine": worst_cos},
+           "bound": "max_abs <= 2e-2, cosine >= 0.9999",
+           "ok": bool(worst_abs <= 2e-2 and worst_cos >= 0.9999)}
+    rec = {"kv": kv, "b200_layer_us": b200_us, "b200_tflops": 4.0 * TPF * kv * HEAD_DIM * HEADS / b200_us / 1e6}
+    try:
+        if not os.path.isdir(REF_DIR):
+            raise RuntimeError("baseline/_ref is not installed")
+        if REF_DIR not in sys.path:
+            sys.path.insert(0, REF_DIR)
+        from lingbot_map.layers.flashinfer_cache import FlashInferKVCacheManager
+        ref = FlashInferKVCacheManager(num_blocks=1, max_num_frames=SCALE_FRAMES + WINDOW + 16, tokens_per_frame=TPF,
+                                       num_heads=HEADS, head_dim=HEAD_DIM, dtype=torch.bfloat16, device=dev,
+                                       num_special_tokens=NSPECIAL, scale_frames=SCALE_FRAMES, sliding_window=WINDOW,
+                                       max_total_frames=n_cached + 100)
+        for t in range(n_cached):
+            ref.append_frame(0, kf[t % 8], vf[t % 8])
+            ref.evict_frames(0, SCALE_FRAMES, WINDOW)
+        assert list(ref.build_visible_page_table(0)) == m.build_visible_page_table(0)
+        fi = ref.compute_attention(0, q)                                   # plans (block 0) and runs
+        run_fi = lambda: ref.prefill_wrapper.run(q=q, paged_kv_cache=ref.kv_caches[0])   # the run() half alone
+        fi_us = time_us(run_fi)
+        rec.update({"flashinfer_layer_us": fi_us, "ratio": fi_us / b200_us,
+                    "flashinfer_tflops": 4.0 * TPF * kv * HEAD_DIM * HEADS / fi_us / 1e6,
+                    "how": "reference FlashInferKVCacheManager from baseline/_ref, backend fa2: plan once, "
+                           f"prefill_wrapper.run timed over {repeats} launches with CUDA events; same page table and K/V"})
+        par["vs_flashinfer_bf16"] = {"elements": int(fi.numel()), "max_abs": float((ours.float() - fi.float()).abs().max()),
+                                     "cosine": _cos64(ours, fi)}
+        del ref
+    except Exception as e:                                                   # noqa: BLE001
+        rec["flashinfer"] = "unavailable: %s: %s" % (type(e).__name__, str(e)[:200])
+    out["flashinfer_layer"], out["parity_at_headline"] = rec, par
+    del m
+    torch.cuda.empty_cache()
+    return out
+
+
+def whole_model_record(args):
+    """Whole GCTStream model (reference code from baseline/_ref) at the 10k-frame cache: frames/s with this backend
+    and with the reference's FlashInfer backend, each in its own process (bench_model.py)."""
+    if not os.path.isdir(REF_DIR):
+        return {"unavailable": "baseline/_ref is not installed"}
+    rec = {"frames_timed": args.whole_model_frames, "cached_frames": args.frames_cached,
+           "how": "bench_model.py: the reference's gct_profile.py model (random init, torch.compile as it does), "
+                  "bf16 autocast, 378x518, cache pre-filled through the manager's own append_frame"}
+    env = dict(os.environ)
+    env["PYTHONPATH"] = os.pathsep.join([ROOT, REF_DIR, env.get("PYTHONPATH", "")])
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        env.pop(k, None)
+    for backend in ("b200", "flashinfer"):
+        cmd = [sys.executable, os.path.join(ROOT, "bench_model.py"), "--reference", REF_DIR, "--backend", backend,
+               "--cached-frames", str(args.frames_cached), "--frames", str(args.whole_model_frames)]
+        try:
+            r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=args.whole_model_timeout)
+            lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+            if r.returncode != 0 or not lines:
+                rec[backend] = {"unavailable": "exit %d: %s" % (r.returncode, (r.stderr or r.stdout)[-300:])}
+                continue
+            d = json.loads(lines[-1])
+            rec[backend + "_fps"] = d["frames_per_s_median"]
+            rec[backend + "_ms_per_frame"] = d["ms_per_frame_median"]
+        except subprocess.TimeoutExpired:
+            rec[backend] = {"unavailable": "timed out after %d s" % args.whole_model_timeout}
+    if "b200_fps" in rec and "flashinfer_fps" in rec:
+        rec["ratio"] = rec["b200_fps"] / rec["flashinfer_fps"]
+    return rec
+
+
 # ----------------------------------------------------------------------------- CPU arm
-def cpu_layer_sample(n_cached, threads):
-    """One global layer + one frame layer of one streaming frame with the CPU port of the reference's SDPA
-    path, at the n_cached-frame steady state.  Returns seconds for the pair."""
-    from oracle import sdpa_port as SP
-    torch.set_num_threads(threads)
-    g = torch.Generator().manual_seed(1)
-    C = HEADS * HEAD_DIM
-    rn = lambda *s: torch.randn(*s, generator=g)
-    params = {"qkv.weight": None, "qkv.bias": None, "proj.weight": None, "proj.bias": None,
-              "q_norm.weight": 1 + 0.1 * rn(64), "q_norm.bias": 0.1 * rn(64),
-              "k_norm.weight": 1 + 0.1 * rn(64), "k_norm.bias": 0.1 * rn(64)}
-    port = SP.SdpaStreamPort(params, HEADS, SCALE_FRAMES, WINDOW, NSPECIAL)
-    # steady state of the dict cache: 72 full frames + specials of the evicted ones (attention.py:676-718)
-    port.k = rn(1, HEADS, SCALE_FRAMES + WINDOW, TPF, HEAD_DIM)
-    port.v = rn(1, HEADS, SCALE_FRAMES + WINDOW, TPF, HEAD_DIM)
-    n_ev = max(n_cached - SCALE_FRAMES - WINDOW, 0)
-    port.k_special = rn(1, HEADS, n_ev, NSPECIAL, HEAD_DIM)
-    port.v_special = rn(1, HEADS, n_ev, NSPECIAL, HEAD_DIM)
-    qkv = rn(1, TPF, 3 * C)
-    cos, sin = SP.rope3d_cos_sin(n_cached % 1024, 1, PPH, PPW, NSPECIAL)
-    import torch.nn.functional as F
+def _reference_layers():
+    """The reference's own SDPAAttention / Attention modules (global and frame layer) from baseline/_ref, or None."""
+    try:
+        if not os.path.isdir(REF_DIR):
+            return None
+        if REF_DIR not in sys.path:
+            sys.path.insert(0, REF_DIR)
+        from lingbot_map.layers.attention import Attention, SDPAAttention
+        from lingbot_map.layers.rope import PositionGetter, RotaryPositionEmbedding2D, WanRotaryPosEmbed
+        return Attention, SDPAAttention, PositionGetter, RotaryPositionEmbedding2D, WanRotaryPosEmbed
+    except Exception:                                                        # noqa: BLE001
+        return None
 
-    def split(t):
-        q, k, v = t.reshape(1, TPF, 3, HEADS, HEAD_DIM).permute(2, 0, 3, 1, 4).unbind(0)
-        q = F.layer_norm(q, (HEAD_DIM,), params["q_norm.weight"], params["q_norm.bias"], 1e-5)
-        k = F.layer_norm(k, (HEAD_DIM,), params["k_norm.weight"], params["k_norm.bias"], 1e-5)
-        return q, k, v
 
-    t0 = time.perf_counter()
-    with torch.no_grad():
-        q, k, v = split(qkv)                                    # global layer (attention.py:601-670, minus Linears)
-        q, k = SP.apply_rope3d(q, cos, sin), SP.apply_rope3d(k, cos, sin)
-        port.attend(q, k, v, 1)
-        q, k, v = split(qkv)                                    # frame layer (attention.py:65-84, minus Linears)
-        q, k = SP.apply_rope3d(q, cos, sin), SP.apply_rope3d(k, cos, sin)   # same cost as the 2-D rotation
-        F.scaled_dot_product_attention(q, k, v)
-    return time.perf_counter() - t0
+class CpuLayerPair:
+    """One global layer + one frame layer of one streaming frame on the host cores, at the n_cached-frame steady
+    state.  kind "reference": the reference's own SDPAAttention (dict KV cache: cat, evict, clone, SDPA; with its
+    qkv/proj Linears, 1.5 % of the layer's flops) and Attention modules, imported from baseline/_ref.
+    kind "port": oracle/sdpa_port.py, the CPU restatement, when the reference package is not installed."""
+
+    def __init__(self, n_cached, threads):
+        torch.set_num_threads(threads)
+        self.n_cached, self.threads = n_cached, threads
+        g = torch.Generator().manual_seed(1)
+        self.rn = rn = lambda *s: torch.randn(*s, generator=g)
+        C = HEADS * HEAD_DIM
+        n_ev = max(n_cached - SCALE_FRAMES - WINDOW, 0)
+        full = min(n_cached, SCALE_FRAMES + WINDOW)
+        self.k = rn(1, HEADS, full, TPF, HEAD_DIM)
+        self.v = rn(1, HEADS, full, TPF, HEAD_DIM)
+        self.ks = rn(1, HEADS, n_ev, NSPECIAL, HEAD_DIM)
+        self.vs = rn(1, HEADS, n_ev, NSPECIAL, HEAD_DIM)
+        ref = _reference_layers()
+        self.kind = "reference" if ref is not None else "port"
+        if ref is not None:
+            Attention, SDPAAttention, PositionGetter, Rope2D, Wan = ref
+            torch.manual_seed(0)
+            self.glob = SDPAAttention(dim=C, num_heads=HEADS, qk_norm=True, rope=object(),
+                                      kv_cache_sliding_window=WINDOW, kv_cache_scale_frames=SCALE_FRAMES).eval()
+            self.frame = Attention(dim=C, num_heads=HEADS, qk_norm=True, rope=Rope2D(frequency=100)).eval()
+            self.pos3d = Wan(attention_head_dim=HEAD_DIM, patch_size=(1, 14, 14), max_seq_len=1024)(
+                ppf=1, pph=PPH, ppw=PPW, patch_start_idx=NSPECIAL, device=torch.device("cpu"),
+                f_start=n_cached % 1024, f_end=n_cached % 1024 + 1)
+            pos = PositionGetter()(1, PPH, PPW, device=torch.device("cpu")) + 1
+            self.pos2d = torch.cat([torch.zeros(1, NSPECIAL, 2, dtype=pos.dtype), pos], dim=1)
+            self.x = rn(1, TPF, C)
+        else:
+            from oracle import sdpa_port as SP
+            self.SP = SP
+            self.params = {"qkv.weight": None, "qkv.bias": None, "proj.weight": None, "proj.bias": None,
+                           "q_norm.weight": 1 + 0.1 * rn(64), "q_norm.bias": 0.1 * rn(64),
+                           "k_norm.weight": 1 + 0.1 * rn(64), "k_norm.bias": 0.1 * rn(64)}
+            self.qkv = rn(1, TPF, 3 * C)
+            self.cos, self.sin = SP.rope3d_cos_sin(n_cached % 1024, 1, PPH, PPW, NSPECIAL)
+
+    def sample(self):
+        """Seconds for the pair; the cache state is rebuilt (views of the same storage) before every sample."""
+        import torch.nn.functional as F
+        if self.kind == "reference":
+            cache = {"k_0": self.k, "v_0": self.v, "k_0_special": self.ks, "v_0_special": self.vs}
+            t0 = time.perf_counter()
+            with torch.no_grad():
+                self.glob(self.x, pos=self.pos3d, enable_3d_rope=True, kv_cache=cache, global_idx=0,
+                          num_frame_per_block=1, num_register_tokens=4)          # attention.py:595-670
+                self.frame(self.x, pos=self.pos2d)                               # attention.py:65-87
+            return time.perf_counter() - t0
+        SP, params = self.SP, self.params
+        port = SP.SdpaStreamPort(params, HEADS, SCALE_FRAMES, WINDOW, NSPECIAL)
+        port.k, port.v, port.k_special, port.v_special = self.k, self.v, self.ks, self.vs
+
+        def split(t):
+            q, k, v = t.reshape(1, TPF, 3, HEADS, HEAD_DIM).permute(2, 0, 3, 1, 4).unbind(0)
+            q = F.layer_norm(q, (HEAD_DIM,), params["q_norm.weight"], params["q_norm.bias"], 1e-5)
+            k = F.layer_norm(k, (HEAD_DIM,), params["k_norm.weight"], params["k_norm.bias"], 1e-5)
+            return q, k, v
+
+        t0 = time.perf_counter()
+        with torch.no_grad():
+            q, k, v = split(self.qkv)                               # global layer (attention.py:601-670, minus Linears)
+            q, k = SP.apply_rope3d(q, self.cos, self.sin), SP.apply_rope3d(k, self.cos, self.sin)
+            port.attend(q, k, v, 1)
+            q, k, v = split(self.qkv)                               # frame layer (attention.py:65-84, minus Linears)
+            q, k = SP.apply_rope3d(q, self.cos, self.sin), SP.apply_rope3d(k, self.cos, self.sin)   # same cost as 2-D
+            F.scaled_dot_product_attention(q, k, v)
+        return time.perf_counter() - t0
+
+    def describe(self):
+        what = ("the reference's SDPAAttention.forward + Attention.forward from baseline/_ref (fp32, dict cache "
+                "cat/evict/clone + SDPA, Linears included)") if self.kind == "reference" else \
+               "oracle/sdpa_port.py (CPU restatement of the reference's SDPA path, Linears excluded)"
+        return (f"1 of {DEPTH} layer pairs (global attention over kv={visible_kv(self.n_cached + 1)} + frame attention "
+                f"1005x1005) x{DEPTH} per frame; {what}; torch CPU, {self.threads} threads")
 
 
 def cpu_baseline(max_seconds=25.0, n_cached=10000):
     threads = os.cpu_count() or 1
+    pair = CpuLayerPair(n_cached, threads)
     times = []
     t_start = time.perf_counter()
     while len(times) < 3 and (not times or time.perf_counter() - t_start + times[-1] < max_seconds):
-        times.append(cpu_layer_sample(n_cached, threads))
+        times.append(pair.sample())
     best = min(times)
-    return {"value": 1.0 / (DEPTH * best), "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"1 of {DEPTH} layer pairs (global attention over kv={visible_kv(n_cached + 1)} fp32 with the "
-                      f"reference's dict cache cat/evict/clone + frame attention 1005x1005), best of {len(times)}, "
-                      f"x{DEPTH} per frame; torch CPU SDPA, {threads} threads",
-            "seconds_per_sample": best}
+    return {"value": 1.0 / (DEPTH * best), "unit": UNIT, "cores": threads, "kind": pair.kind,
+            "sample": pair.describe() + f", best of {len(times)}", "seconds_per_sample": best}
 
 
 def run_reference(args):
@@ -401,21 +742,21 @@ def run_reference(args):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
+    pair = CpuLayerPair(args.frames_cached, threads)
     for _ in range(min(args.warmup, 1)):
-        cpu_layer_sample(args.frames_cached, threads)
+        pair.sample()
     steps = min(args.steps, 8)            # each step is a bounded sample: 1 of 24 layer pairs
-    t = [cpu_layer_sample(args.frames_cached, threads) for _ in range(steps)]
+    t = [pair.sample() for _ in range(steps)]
     per_frame = DEPTH * (sum(t) / len(t))
     value = 1.0 / per_frame
-    cb = {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
-          "sample": f"each step = 1 of {DEPTH} layer pairs at kv={visible_kv(args.frames_cached + 1)}, x{DEPTH}; "
-                    f"{steps} steps timed (capped at 8 to stay within minutes)"}
+    cb = {"value": value, "unit": UNIT, "cores": threads, "kind": pair.kind,
+          "sample": pair.describe() + f"; {steps} steps timed (capped at 8 to stay within minutes)"}
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": min(args.warmup, 1), "ms_per_step": per_frame * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "CPU port of the reference's SDPA streaming path (oracle/sdpa_port.py), same frame "
-                               f"geometry and {args.frames_cached}-frame cache state as the GPU arm", "cores": threads},
+        "config": {"workload": "the reference's CPU (SDPA dict-cache) streaming path, same frame geometry and "
+                               f"{args.frames_cached}-frame cache state as the GPU arm", "cores": threads},
         "cpu_baseline": cb,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
@@ -425,13 +766,22 @@ def main():
     global DEPTH, SCALE_FRAMES, WINDOW
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=160)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--mode", default="streams", choices=["streams", "kvsplit"])
+    ap.add_argument("--streams-per-gpu", type=int, default=1,
+                    help="independent streams per GPU, interleaved step by step on one CUDA stream")
     ap.add_argument("--frames-cached", type=int, default=10000)
-    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--kernel-steps", type=int, default=20,
+                    help="steps of the second pass that brackets every attention launch with CUDA events")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-flashinfer", action="store_true", help="skip the same-box FlashInfer layer timing + parity record")
+    ap.add_argument("--no-whole-model", action="store_true", help="skip the whole-model frames/s of both backends")
+    ap.add_argument("--no-kvsplit", action="store_true", help="N > 1: skip the KV-sharded single-stream sub-record")
+    ap.add_argument("--whole-model-frames", type=int, default=40)
+    ap.add_argument("--whole-model-timeout", type=int, default=420)
     ap.add_argument("--exact-softmax", action="store_true",
                     help="force the attention instantiation that tracks the running row maximum (bounded mode off)")
     ap.add_argument("--scale-frames", type=int, default=SCALE_FRAMES,

@@ -1,7 +1,9 @@
 """Whole-model streaming frames/s of the reference's GCTStream at a pre-filled KV cache, with either backend.
 
-    python -m lingbot_map_b200.model_bench --reference <dir holding the lingbot_map package and gct_profile.py> \
+    python bench_model.py --reference <dir holding the lingbot_map package and gct_profile.py> \
         --backend b200|flashinfer --cached-frames 10000 --frames 40 [--no-compile]
+
+A measurement tool beside bench.py (which runs it for its `whole_model` record); not part of the importable package.
 
 The model, its random-init weights, the synthetic images (randn, seed 42), bf16 autocast and the optional
 torch.compile of the hot modules are the ones of the reference's gct_profile.py (load_model / compile_model are
@@ -73,7 +75,8 @@ def main(argv=None):
 
     gp = _load_profile_module(os.path.abspath(args.reference))
     if args.backend == "b200":
-        from . import select
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from lingbot_map_b200 import select
         select.install(patch_embed_attention=args.patch_embed)
     torch.manual_seed(0)
     model = gp.load_model("flashinfer", img_size=518, sliding_window=64, max_frame_num=args.cached_frames + 400,

@@ -76,7 +76,10 @@ int gct_mgr_destroy(gct_mgr_t* m);
 /* Hand the manager the caller-allocated device memory: one bf16 pool per block laid out
  * [max_num_pages, 2 (K,V), page_size, H, 64] (flashinfer_cache.py:141-148) and a workspace for
  * split-KV partial results, the device page table and the status word (the reference's
- * workspace_buffer, flashinfer_cache.py:184-186).  Needs a CUDA device. */
+ * workspace_buffer, flashinfer_cache.py:184-186).  Needs a CUDA device.
+ * Every row of a pool must hold finite values, also rows that no append has written yet: the attention kernel reads
+ * whole 128-token blocks, masks the rows past the valid length of a page, and multiplies their (zero) weights with
+ * whatever V holds there - zero-initialise the pools (0 * NaN would be NaN). */
 int gct_mgr_bind(gct_mgr_t* m, void* const* pools_dev, void* workspace_dev, size_t workspace_bytes);
 /* Smallest workspace gct_mgr_bind accepts for this geometry. */
 int gct_mgr_workspace_bytes(const gct_mgr_t* m, size_t* bytes_out);
@@ -211,6 +214,10 @@ int gct_lse_merge_strided(const float* parts_dev, const float* lse_dev, int grou
  * The first call on a device looks up the array's address on that device (cudaGetSymbolAddress); make
  * that first call before any stream capture begins.  All calls on a GPU share the array: calls whose
  * GPU work can overlap (several streams or host threads) race and must be serialised by the caller.
+ * The pool belongs to the caller: every row of a visible page must hold finite values, also the rows of the last
+ * page past last_page_len (they are read, masked, and their zero weights multiplied with what V holds there).
+ * visible_pages_host is copied to the GPU by an asynchronous copy on `stream`: if it is pinned memory it must
+ * stay alive and unchanged until `stream` has passed the call (pageable memory is staged before the call returns).
  * device_status_out may be NULL; otherwise the call synchronises `stream` and stores the kernels'
  * status word (0 = ok). */
 int gct_attn_paged_static(const void* pool_dev, int max_num_pages, int page_size, int heads,

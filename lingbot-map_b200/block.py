@@ -20,8 +20,17 @@ from . import _lib, ops
 from .cache import B200KVCacheManager
 
 
+def _reference_classes():
+    """(FlashInferBlock, FlashInferAttention) of the reference package, for the one mode this backend hands back to
+    it: a cache manager that is not a B200KVCacheManager (the reference's fp32 gather + SDPA comparison mode)."""
+    from lingbot_map.layers.attention import FlashInferAttention
+    from lingbot_map.layers.block import FlashInferBlock
+    return FlashInferBlock, FlashInferAttention
+
+
 class LayerScale(nn.Module):
-    """x * gamma (lingbot_map/layers/layer_scale.py)."""
+    """x * gamma (lingbot_map/layers/layer_scale.py).  The parameter name `gamma` is fixed by the checkpoint; the
+    module is the usual timm / DINOv2 one-liner, restated here so that the block imports without the reference."""
 
     def __init__(self, dim: int, init_values: float = 1e-5, inplace: bool = False) -> None:
         super().__init__()
@@ -33,7 +42,7 @@ class LayerScale(nn.Module):
 
 
 class Mlp(nn.Module):
-    """fc1 -> act -> fc2 (lingbot_map/layers/mlp.py)."""
+    """fc1 -> act -> fc2 (lingbot_map/layers/mlp.py); sub-module names fixed by the checkpoint, as above."""
 
     def __init__(self, in_features: int, hidden_features: Optional[int] = None, out_features: Optional[int] = None,
                  act_layer: Callable[..., nn.Module] = nn.GELU, drop: float = 0.0, bias: bool = True) -> None:
@@ -151,6 +160,8 @@ class B200Attention(_AttentionBase):
 
     def prepare_qkv(self, x: Tensor, pos=None, enable_3d_rope: bool = False) -> tuple:
         """(q, k, v), each [tokens, H, 64] bf16 - same contract as attention.py:402-426 (B = 1)."""
+        if getattr(self, "_reference_manager", False):      # fp32 comparison mode: the reference's own arithmetic
+            return _reference_classes()[1].prepare_qkv(self, x, pos=pos, enable_3d_rope=enable_3d_rope)
         cs, mode = self._rope_args(pos, enable_3d_rope)
         return ops.prep_qkv(self._qkv_rows(x), self.num_heads, x.shape[1], *self._norm_params(), cs, mode)
 
@@ -177,6 +188,14 @@ class B200Attention(_AttentionBase):
                 enable_3d_rope=False, kv_cache=None, global_idx=0, num_frame_per_block=1, num_frame_for_scale=-1,
                 num_register_tokens=4) -> Tensor:
         B, N, C = x.shape
+        if kv_cache is not None and not isinstance(kv_cache, B200KVCacheManager):
+            # a manager of the reference's own class (fp32 comparison mode): its attention layer's code on this module
+            self._reference_manager = True
+            return _reference_classes()[1].forward(
+                self, x, pos=pos, num_patches=num_patches, num_special=num_special, num_frames=num_frames,
+                enable_3d_rope=enable_3d_rope, kv_cache=kv_cache, global_idx=global_idx,
+                num_frame_per_block=num_frame_per_block, num_frame_for_scale=num_frame_for_scale,
+                num_register_tokens=num_register_tokens)
         if not isinstance(kv_cache, B200KVCacheManager):
             # batch mode (attention.py:446-465): dense attention over all N tokens of each batch entry
             out, _, _ = self._dense(x, pos, enable_3d_rope, tokens_per_frame=N)
@@ -226,17 +245,49 @@ class B200Block(nn.Module):
         self.sample_drop_ratio = drop_path
 
     def attn_pre(self, x: Tensor, pos=None, enable_3d_rope: bool = False) -> tuple:
-        """norm1 + prepare_qkv (block.py:217-227).  Kept for callers that rebind or call it; the streaming
-        forward below uses the fused append instead, which writes K/V straight into their pages."""
+        """norm1 + prepare_qkv (block.py:217-227): (q, k, v), each [tokens, H, 64].  The reference's compile_model
+        rebinds this attribute to a torch.compile'd callable (gct_profile.py:51-56, demo.py:181-186); the streaming
+        forward below then goes through it, so that norm1 and the qkv Linear stay inside the caller's compiled
+        region (the q/k norm + RoPE kernel is traced as the custom operator gct_b200::prep_qkv).  While it is not
+        rebound the forward uses the fused append, which writes K/V straight into their pages."""
         return self.attn.prepare_qkv(self.norm1(x), pos=pos, enable_3d_rope=enable_3d_rope)
+
+    def _stream_through_attn_pre(self, x, pos, enable_3d_rope, manager, global_idx, num_register_tokens):
+        """Streaming frame with the caller's (compiled) attn_pre: block.py:245-282 on this backend's manager."""
+        q, k, v = self.attn_pre(x, pos=pos, enable_3d_rope=enable_3d_rope)
+        if getattr(manager, "_skip_append", False):
+            prev_defer = manager._defer_eviction
+            manager._defer_eviction = True
+            manager.append_frame(global_idx, k, v)
+            out = manager.compute_attention(global_idx, q)
+            manager.rollback_last_frame(global_idx)
+            manager._defer_eviction = prev_defer
+        else:
+            manager.append_frame(global_idx, k, v)
+            self.attn._evict(manager, global_idx, num_register_tokens)
+            out = manager.compute_attention(global_idx, q)
+        return out.reshape(x.shape[0], q.shape[0], self.attn.num_heads * self.attn.head_dim)
 
     def forward(self, x: Tensor, pos=None, num_patches=None, num_special=None, num_frames=None, enable_3d_rope=False,
                 kv_cache=None, global_idx=0, num_frame_per_block=1, num_frame_for_scale=-1,
                 num_register_tokens=4) -> Tensor:
+        if kv_cache is not None and not isinstance(kv_cache, B200KVCacheManager):
+            # the reference's own manager (force_fp32, its fp32 gather + SDPA comparison mode): run the reference's
+            # block code on this module's parameters; nothing of this backend computes in that mode
+            self.attn._reference_manager = True
+            return _reference_classes()[0].forward(
+                self, x, pos=pos, num_patches=num_patches, num_special=num_special, num_frames=num_frames,
+                enable_3d_rope=enable_3d_rope, kv_cache=kv_cache, global_idx=global_idx,
+                num_frame_per_block=num_frame_per_block, num_frame_for_scale=num_frame_for_scale,
+                num_register_tokens=num_register_tokens)
         is_streaming = kv_cache is not None and (num_frames is None or num_frames <= 1)
         if is_streaming:
-            attn_x = self.attn.stream_frame(self.norm1(x), pos, enable_3d_rope, kv_cache, global_idx,
-                                            num_register_tokens)
+            if "attn_pre" in self.__dict__:      # rebound by the caller (compile_model): keep its compiled region
+                attn_x = self._stream_through_attn_pre(x, pos, enable_3d_rope, kv_cache, global_idx,
+                                                       num_register_tokens)
+            else:
+                attn_x = self.attn.stream_frame(self.norm1(x), pos, enable_3d_rope, kv_cache, global_idx,
+                                                num_register_tokens)
             if attn_x.dtype != x.dtype and not torch.is_autocast_enabled():
                 attn_x = attn_x.to(x.dtype)
             x = x + self.ls1(self.attn.proj(attn_x))

@@ -19,6 +19,19 @@
 //   MMA       wait s_empty, K_{j+1}: issue S_{j+1} (runs under the softmax of block j) -> s_full, k_empty
 //             wait p_full,  V_j    : issue O += P_j V_j                                -> pv_full, v_empty
 // Every mbarrier wait is bounded and reports through the status word instead of spinning forever.
+//
+// Bounded mode (gct_attn_kernel<2, true>, paged attention through the cache manager).  key_norm_max[h] bounds the
+// 2-norm of every key of head h in the cache, so ref = |q_row| * key_norm_max[h] bounds every logit of the row
+// (Cauchy-Schwarz) and can stand in for the running row maximum while it is small.  The softmax threads prepare
+// this once per CTA from the Q tile in shared memory: they multiply their row by scale * log2(e) in place,
+// derive ref from the scaled row, and write two small operand tiles, Qx (column 0 = -ref) and Kx (column 0 = 1).
+// A fifth K16 step of the S product, S += Qx Kx^T, then subtracts ref inside the tensor core: S arrives in TMEM
+// as the finished base-2 exponent, and the sweep is exp2, row sum and bf16 packing only - no row maximum, no
+// multiply-add in front of the exponential, no rescale of O.  A CTA in which some row's ref exceeds the limit
+// (or is not finite) takes a compact two-pass softmax with a running maximum instead; the choice is made per
+// CTA inside the one launch.
+#include <mutex>
+
 #include "gct_common.h"
 
 namespace gct {
@@ -181,6 +194,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+// 16 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -206,6 +228,30 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
   r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
   return r;
 }
+// Same for exponents known to lie in [-126, 1]: no clamp.  kDeg 3: relative error 7.7e-5; kDeg 2: 1.8e-3.
+// `shift` (a non-negative integer value) is subtracted from the exponent first, at no cost: it rides in the rounding
+// constant.
+template <int kDeg>
+__device__ __forceinline__ float2 exp2_poly2_inrange(float2 x, float shift = 0.f) {
+  constexpr float kMagic = 12582912.f;
+  const float ms = kMagic - shift;                       // exact: both are integers below 2^24
+  const float2 t = __fadd2_rn(x, make_float2(ms, ms));   // 1.5 * 2^23 + round(x - shift)
+  const float2 n = __fadd2_rn(t, make_float2(-ms, -ms)); // round(x - shift) + shift
+  const float2 f = __fadd2_rn(x, make_float2(-n.x, -n.y));
+  float2 p;
+  if constexpr (kDeg == 3) {
+    p = __ffma2_rn(make_float2(0.0551716648f, 0.0551716648f), f, make_float2(0.2426111251f, 0.2426111251f));
+    p = __ffma2_rn(p, f, make_float2(0.6932609677f, 0.6932609677f));
+    p = __ffma2_rn(p, f, make_float2(0.9999280572f, 0.9999280572f));
+  } else {
+    p = __ffma2_rn(make_float2(0.23783042f, 0.23783042f), f, make_float2(0.70339652f, 0.70339652f));
+    p = __ffma2_rn(p, f, make_float2(1.0005137f, 1.0005137f));
+  }
+  float2 r;
+  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -226,13 +272,11 @@ struct KernelArgs {
   float* part_o;
   float* part_lse;
   int* status;
-  // Bounded mode (see gct_row_ref_kernel): row_ref[row] >= every scaled logit of the row, so it serves as a fixed
-  // softmax reference and the kernel needs neither row maxima nor rescaling.  *unsafe_epoch == epoch means that the
-  // bound of some row was too loose: the bounded kernel then returns at once and the exact kernel does the work;
-  // otherwise the exact kernel returns at once.  unsafe_epoch == nullptr: exact kernel only.
-  const float* row_ref;
-  const int* unsafe_epoch;
-  int epoch;
+  // Bounded mode: key_norm_max[h] >= the 2-norm of every key of head h that the page table can reach;
+  // bounded_limit is the largest row reference (in base-2 exponent units) a CTA accepts before it falls back
+  // to the running-maximum softmax.  Null: the kernel instantiation without the bounded mode is launched.
+  const float* key_norm_max;
+  float bounded_limit;
 };
 
 constexpr int kKStages = 4;
@@ -257,14 +301,45 @@ constexpr int kSumLag = GCT_SUM_LAG;
 #endif
 constexpr int kPvWaitAt = GCT_PV_WAIT_AT;    // pair (31..61) after which the sweep waits for the previous PV and stores P[0,64)
 constexpr int kMaxChains = GCT_MAX_CHAINS;
-#ifndef GCT_BOUNDED_OVERLAP
-#define GCT_BOUNDED_OVERLAP 1
+// Bounded mode: pair q of the sweep takes the polynomial when floor((q+1) * NUM / DEN) != floor(q * NUM / DEN),
+// i.e. NUM of every DEN pairs, evenly spread; the rest go to the special-function unit.
+#ifndef GCT_BOUNDED_POLY_NUM
+#define GCT_BOUNDED_POLY_NUM 2
 #endif
-#ifndef GCT_POLY_EVERY_BOUNDED
-#define GCT_POLY_EVERY_BOUNDED GCT_POLY_EVERY
+#ifndef GCT_BOUNDED_POLY_DEN
+#define GCT_BOUNDED_POLY_DEN 5
 #endif
-constexpr int kPolyEveryBounded = GCT_POLY_EVERY_BOUNDED;    // share of polynomial exponentials in bounded mode
-constexpr bool kBoundedOverlap = GCT_BOUNDED_OVERLAP != 0;   // bounded mode: sweep the first half while the second loads
+#ifndef GCT_BOUNDED_POLY_DEG
+#define GCT_BOUNDED_POLY_DEG 3
+#endif
+#ifndef GCT_BOUNDED_HALF_AT
+#define GCT_BOUNDED_HALF_AT 28
+#endif
+constexpr int kBoundedPolyNum = GCT_BOUNDED_POLY_NUM, kBoundedPolyDen = GCT_BOUNDED_POLY_DEN;
+constexpr int kBoundedPolyDeg = GCT_BOUNDED_POLY_DEG;
+constexpr int kBoundedHalfAt = GCT_BOUNDED_HALF_AT;   // pair before which the second half of the S row must have landed
+static_assert(kBoundedHalfAt >= 0 && kBoundedHalfAt <= 32, "the second half of the row is needed from pair 32 on");
+// 1: P of a block is announced to the MMA warp as soon as its stores have completed, at the end of the block's
+// iteration; 0: by the next iteration, after it has issued its first S loads (hides the store latency, but the
+// PV product then starts later and its completion is waited for in the middle of the next sweep).
+#ifndef GCT_EARLY_P_FULL
+#define GCT_EARLY_P_FULL 1
+#endif
+// 1: the row reference is subtracted by a fifth K16 step of the S product (Qx Kx^T); 0: by the softmax threads
+// (the reference is then rounded up to an integer, which the polynomial exponentials absorb into their rounding
+// constant for free; only the pairs that go to the special-function unit pay a packed add).
+#ifndef GCT_BOUNDED_FOLD
+#define GCT_BOUNDED_FOLD 1
+#endif
+constexpr bool kBoundedFold = GCT_BOUNDED_FOLD != 0;
+constexpr bool kEarlyPFull = GCT_EARLY_P_FULL != 0;
+// 1: the waits inside the KV loop of the softmax warps end with a warp vote.  The outcome of a wait is the same in
+// every lane without it: the lanes of a converged warp poll one mbarrier phase, one clock and one abort word with the
+// same instructions, so they all see the same values; the vote costs 1.3 % of the kernel and is kept for the waits
+// outside the loop only.
+#ifndef GCT_VOTE_WAITS
+#define GCT_VOTE_WAITS 0
+#endif
 // Register budget at two query tiles per CTA: 384 threads start with 168 registers each (64512 in total);
 // the control warpgroup shrinks to kControlRegs and the two softmax warpgroups grow to kSoftmaxRegs:
 // 128 * kControlRegs + 256 * kSoftmaxRegs <= 64512, both multiples of 8.
@@ -284,9 +359,13 @@ struct SmemLayout {
   static constexpr uint32_t q_off = 0;
   static constexpr uint32_t k_off = q_off + QT * kTileBytes;
   static constexpr uint32_t v_off = k_off + kKStages * kTileBytes;
-  static constexpr uint32_t bar_off = v_off + kVStages * kTileBytes;
-  // barriers: q_full, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], then per tile s_full, s_empty, p_full, pv_full
-  static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 4 * QT;
+  // bounded mode (QT == 2): one more 128B-swizzled 128 x 64 tile whose K16 column groups hold the extra operands
+  // of the S product: bf16 columns [0,16) Qx of tile 0, [16,32) Qx of tile 1, [32,48) Kx
+  static constexpr uint32_t x_off = v_off + kVStages * kTileBytes;
+  static constexpr uint32_t bar_off = x_off + (QT == 2 ? kTileBytes : 0);
+  // barriers: q_full, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], per tile s_full, s_empty, p_full, pv_full,
+  // then q_ready (bounded mode: Q scaled, Qx and Kx written)
+  static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 4 * QT + 1;
   static constexpr uint32_t misc_off = bar_off + n_bars * 8;
   static constexpr uint32_t total = misc_off + 16;
 };
@@ -302,10 +381,7 @@ __global__ void __launch_bounds__(kThreads<QT>, 1)
 gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const KernelArgs a) {
   using L = SmemLayout<QT>;
-  if (a.unsafe_epoch != nullptr) {
-    const bool unsafe = *a.unsafe_epoch == a.epoch;
-    if (unsafe == kBounded) return;              // the other instantiation handles this launch
-  }
+  static_assert(!kBounded || QT == 2, "the bounded mode exists for two query tiles per CTA");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -320,8 +396,10 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   auto bar_s_empty = [&](int t) { return bars + 8u * (kTileBars + 4 * t + 1); };
   auto bar_p_full = [&](int t) { return bars + 8u * (kTileBars + 4 * t + 2); };
   auto bar_pv_full = [&](int t) { return bars + 8u * (kTileBars + 4 * t + 3); };
+  auto bar_q_ready = [&]() { return bars + 8u * (kTileBars + 4 * QT); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::misc_off);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(smem + L::misc_off + 4);
+  volatile int* cta_unsafe = reinterpret_cast<volatile int*>(smem + L::misc_off + 8);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -360,7 +438,9 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(bar_p_full(t), 4);
       mbar_init(bar_pv_full(t), 1);
     }
+    mbar_init(bar_q_ready(), 4 * QT);            // one arrival per softmax warp
     *cta_abort = 0;
+    *cta_unsafe = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kFirstMmaWarp) {
@@ -416,6 +496,10 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int k = 0; k < 4; ++k)   // 64 = 4 x K16; +32 B per step inside the 128 B swizzle row
           umma_ss(lead, tmem_base + t * 128, ad + 2 * k, bd + 2 * k, kIdescS, k > 0);
+        if constexpr (kBounded && kBoundedFold) {     // S += Qx_t Kx^T: subtracts the row reference (column groups t and 2 of the x tile)
+          const uint64_t xd = smem_desc(sbase + L::x_off, 16, 1024);
+          umma_ss(lead, tmem_base + t * 128, xd + 2 * t, xd + 4, kIdescS, 1u);
+        }
       };
       auto issue_pv = [&](int vs, uint32_t accumulate) {
 #pragma unroll
@@ -428,7 +512,7 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
         return __all_sync(0xffffffffu, mbar_wait(bar, parity, cta_abort, a.status));
       };
-      bool ok = wait(bar_q_full(), 0) && wait(bar_k_full(0), 0);
+      bool ok = wait(kBounded ? bar_q_ready() : bar_q_full(), 0) && wait(bar_k_full(0), 0);
       if (ok) {
         tc_fence_after();
         issue_s(0);
@@ -463,20 +547,151 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t s_addr = tmem_base + lane_addr + t * 128;
     const uint32_t o_addr = tmem_base + lane_addr + kOCol + t * 64;
     const uint32_t p_addr = tmem_base + lane_addr + kPCol + t * 64;
-    const float c = a.scale_log2;
+    const float c = kBounded ? 1.f : a.scale_log2;  // bounded mode: the Q tile already carries scale * log2(e)
     float m = -INFINITY, l = 0.f;                   // m: reference maximum (raw logit units)
-    float ref_fixed = 0.f;                          // bounded mode: upper bound of this row's scaled logits
-    if constexpr (kBounded) {
-      const int qr = (qg * QT + t) * kTileM + row;
-      ref_fixed = a.row_ref[(static_cast<size_t>(b) * a.n_q + (qr < a.n_q ? qr : 0)) * a.heads + h];
-    }
+    float ref_fixed = 0.f;                          // bounded mode: upper bound of this row's exponents
     bool ok = true;
+    bool running_max = false;                       // bounded kernel: this CTA fell back to the running maximum
+    // waits whose outcome the whole warp shares (the tcgen05 loads and stores that follow are warp-wide): with a
+    // vote outside the KV loop, by construction inside it (see GCT_VOTE_WAITS)
+    auto wait_v = [&](uint32_t bar, uint32_t parity) -> bool {
+      return __all_sync(0xffffffffu, mbar_wait(bar, parity, cta_abort, a.status));
+    };
+    auto wait_u = [&](uint32_t bar, uint32_t parity) -> bool {
+#if GCT_VOTE_WAITS
+      return __all_sync(0xffffffffu, mbar_wait(bar, parity, cta_abort, a.status));
+#else
+      return mbar_wait(bar, parity, cta_abort, a.status);
+#endif
+    };
+
+    if constexpr (kBounded) {
+      // ---- once per CTA: scale the Q row in place, derive its reference, write Qx and Kx ----
+      ok = wait_v(bar_q_full(), 0);
+      const uint32_t q_row = sbase + L::q_off + t * kTileBytes + row * 128;
+      const uint32_t swz = static_cast<uint32_t>(row & 7);
+      float sq = 0.f;
+      if (ok) {
+        const float cs = a.scale_log2;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {              // 16-byte chunk j of the row sits at chunk j ^ (row & 7)
+          const uint32_t addr = q_row + ((static_cast<uint32_t>(j) ^ swz) << 4);
+          uint32_t w[4];
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float lo = __uint_as_float(w[i] << 16) * cs, hi = __uint_as_float(w[i] & 0xffff0000u) * cs;
+            w[i] = pack_bf16x2(lo, hi);
+            const float rlo = __uint_as_float(w[i] << 16), rhi = __uint_as_float(w[i] & 0xffff0000u);
+            sq = fmaf(rlo, rlo, fmaf(rhi, rhi, sq));
+          }
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+        }
+        // rounded up to bf16 (the precision of the Qx operand) so that the value used is still an upper bound
+        const float ref = sqrtf(sq) * __ldg(a.key_norm_max + h);
+        if (!(ref <= a.bounded_limit)) *cta_unsafe = 1;            // too loose, infinite or NaN
+        ref_fixed = kBoundedFold ? __uint_as_float((__float_as_uint(ref) + 0xffffu) & 0xffff0000u) : ceilf(ref);
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(128 * QT) : "memory");   // all softmax threads, also after a failed wait
+      running_max = *cta_unsafe != 0;
+      if (running_max) ref_fixed = 0.f;
+      if (ok && !kBoundedFold) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the scaled Q rows -> tensor-core reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_q_ready());
+      }
+      if (ok && kBoundedFold) {
+        const uint32_t x_row = sbase + L::x_off + row * 128;
+        const uint32_t negref = running_max ? 0u : ((__float_as_uint(ref_fixed) >> 16) | 0x8000u);
+        auto st_chunk = [&](int j, uint32_t first) {
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %2, %2};" ::"r"(x_row + ((static_cast<uint32_t>(j) ^ swz) << 4)),
+                       "r"(first), "r"(0u) : "memory");
+        };
+        st_chunk(2 * t, negref);                   // Qx_t: column 0 = -ref, columns 1..15 = 0
+        st_chunk(2 * t + 1, 0u);
+        if (t == 0) {                              // Kx: column 0 = 1
+          st_chunk(4, 0x3f80u);
+          st_chunk(5, 0u);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_q_ready());
+      }
+    }
     uint32_t s[128];
 
     int pi = g0 / a.blocks_per_page;               // page and block-in-page of block j, advanced incrementally
     int jb = g0 - pi * a.blocks_per_page;
-    for (int j = 0; j < nblk; ++j) {
-      if (!(ok = mbar_wait(bar_s_full(t), j & 1, cta_abort, a.status))) break;
+    if (kBounded && running_max) {
+      // ---- fallback of the bounded kernel: two passes over the S row in TMEM, 32 columns at a time ----
+      // pass 1 takes the masked row maximum, pass 2 exponentiates against the running maximum (moved only when the
+      // row maximum outgrows it by 2^kRescaleThreshold) and stores P; compact rather than fast.
+      for (int j = 0; ok && j < nblk; ++j) {
+        if (!(ok = wait_v(bar_s_full(t), j & 1))) break;
+        tc_fence_after();
+        const int plen = (pi == a.n_pages - 1) ? a.last_page_len : a.page_len;
+        const int valid = min(kBlockN, plen - jb * kBlockN);
+        if (++jb == a.blocks_per_page) {
+          jb = 0;
+          ++pi;
+        }
+        uint32_t r[32];
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+          tmem_ld32(s_addr + 32 * ch, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (32 * ch + i < valid) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+        float alpha = 1.f;
+        if (mx - m > kRescaleThreshold) {            // always true on the first block (m = -inf)
+          alpha = fast_exp2(m - mx);
+          m = mx;
+        }
+        if (j > 0) {
+          if (!(ok = wait_v(bar_pv_full(t), (j - 1) & 1))) break;
+          tc_fence_after();
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+            for (int hh = 0; hh < 2; ++hh) {
+              tmem_ld32(o_addr + hh * 32, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st32(o_addr + hh * 32, r);
+            }
+          }
+        }
+        float sum = 0.f;
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+          tmem_ld32(s_addr + 32 * ch, r);
+          tmem_wait_ld();
+          uint32_t pk16[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int col = 32 * ch + 2 * i;
+            const float e0 = col < valid ? fast_exp2(__uint_as_float(r[2 * i]) - m) : 0.f;
+            const float e1 = col + 1 < valid ? fast_exp2(__uint_as_float(r[2 * i + 1]) - m) : 0.f;
+            sum += e0 + e1;
+            pk16[i] = pack_bf16x2(e0, e1);
+          }
+          tmem_st16(p_addr + 16 * ch, pk16);
+        }
+        l = fmaf(l, alpha, sum);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bar_s_empty(t));               // S was read twice: only now may the next block overwrite it
+          mbar_arrive(bar_p_full(t));
+        }
+      }
+    } else
+    for (int j = 0; ok && j < nblk; ++j) {
+      if (!(ok = wait_u(bar_s_full(t), j & 1))) break;
       tc_fence_after();
       // valid tokens of this block
       const int plen = (pi == a.n_pages - 1) ? a.last_page_len : a.page_len;
@@ -485,14 +700,19 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         jb = 0;
         ++pi;
       }
+      // keys past the valid length: -inf (exp2 gives 0); bounded mode: an exponent the polynomial can take
+      // (without the fold the reference is still to be subtracted from it)
+      const uint32_t kMaskBits = !kBounded ? 0xff800000u : (kBoundedFold ? 0xc2fc0000u /* -126.f */ : __float_as_uint(ref_fixed - 126.f));
       // masked maximum of s[lo, lo+64): four independent chains of 3-input max
       auto half_max = [&](int lo) -> float {
         if (valid < lo + 64) {
 #pragma unroll
           for (int i = 0; i < 64; ++i)
-            if (lo + i >= valid) s[lo + i] = 0xff800000u;   // -inf: exp2 gives 0
+            if (lo + i >= valid) s[lo + i] = kMaskBits;
         }
-        if constexpr (kBounded) return 0.f;       // the reference is fixed: only the masking above is needed
+        if constexpr (kBounded) {
+          return 0.f;                             // the reference is fixed: only the masking above is needed
+        } else {
         // kMaxChains independent chains of 3-input max, merged by a tree at the end
         float mxc[kMaxChains];
 #pragma unroll
@@ -518,6 +738,7 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int ch = 0; ch < w; ++ch) mxc[ch] = fmaxf(mxc[ch], mxc[ch + w]);
         return mxc[0];
+        }
       };
       // the second half of the row is still arriving from TMEM while the first half is reduced
       float mx;
@@ -528,26 +749,42 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint32_t(&s3)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[96]);
         tmem_ld32(s_addr, s0);
         tmem_ld32(s_addr + 32, s1);
-        if (j > 0) {
+        if (j > 0 && !(kBounded && kEarlyPFull)) {
           // P of the previous block: its stores completed while the loads above were issued
           tmem_wait_st();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_p_full(t));
         }
-        tmem_wait_ld();
-        tmem_ld32(s_addr + 64, s2);
-        tmem_ld32(s_addr + 96, s3);
+        if constexpr (kBounded && kBoundedHalfAt == 0) {
+          // the whole row at once (a row takes under a hundred clocks to arrive): S is released right away
+          tmem_ld32(s_addr + 64, s2);
+          tmem_ld32(s_addr + 96, s3);
+          tmem_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_s_empty(t));
+          if (valid < 128) {
+#pragma unroll
+            for (int i = 64; i < 128; ++i)
+              if (i >= valid) s[i] = kMaskBits;
+          }
+        } else {
+          tmem_wait_ld();
+          tmem_ld32(s_addr + 64, s2);
+          tmem_ld32(s_addr + 96, s3);
+        }
         const float mlo = half_max(0);
-        if constexpr (!(kBounded && kBoundedOverlap)) {
+        if constexpr (!kBounded) {
           tmem_wait_ld();
           // the S tile is in registers: the tensor core may overwrite it with the next block
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_s_empty(t));
+          mx = fmaxf(mlo, half_max(64));
+        } else {
+          mx = mlo;                                // unused: the second half is masked after its load, inside the sweep
         }
-        if constexpr (kBounded && kBoundedOverlap) mx = mlo;   // the second half is masked after its load, in the sweep
-        else mx = fmaxf(mlo, half_max(64));
       }
       // move the reference maximum only when the row maximum outgrew it by more than 2^kRescaleThreshold;
       // until then exponentials stay below 2^8 and every sum remains exact enough in fp32
@@ -558,14 +795,14 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           m = mx;
         }
       }
-      const float mc = kBounded ? ref_fixed : m * c;
+      const float mc = m * c;                        // bounded mode: unused, the tensor core already subtracted ref
 
       // P (and O) of this tile are free once the PV product of the previous block has completed.  The wait
       // sits in the middle of the exponential sweep, right before the first store of P, so that the
       // round trip softmax -> MMA warp -> tensor core -> mbarrier hides under the first half of the sweep.
       auto wait_prev_pv_and_rescale = [&]() -> bool {
         if (j > 0) {
-          if (!mbar_wait(bar_pv_full(t), (j - 1) & 1, cta_abort, a.status)) return false;
+          if (!wait_u(bar_pv_full(t), (j - 1) & 1)) return false;
           tc_fence_after();
           if (!kBounded && __any_sync(0xffffffffu, alpha != 1.f)) {   // rare: rescale this warp's 32 rows of O in TMEM
             uint32_t ob[32];
@@ -584,22 +821,34 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // P = exp2(S*c - m*c), software-pipelined over pairs of logits so that the exponentials (the scarce
       // pipe) are interleaved with independent work: pair p+4 gets its packed FFMA, pair p its two EX2,
       // pair p-2 its packed add into the row sum and its bf16 conversion (two K values per TMEM column).
+      // Bounded mode: S already is the exponent, the packed FFMA is gone.
       const float2 c2 = make_float2(c, c), nmc2 = make_float2(-mc, -mc);
       float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
       uint32_t pk[kPvWaitAt > 31 ? 64 : 32];
       auto pair_ffma = [&](int q) {
-        const float2 x = __ffma2_rn(make_float2(__uint_as_float(s[2 * q]), __uint_as_float(s[2 * q + 1])), c2, nmc2);
-        s[2 * q] = __float_as_uint(x.x);
-        s[2 * q + 1] = __float_as_uint(x.y);
+        if constexpr (!kBounded) {
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(s[2 * q]), __uint_as_float(s[2 * q + 1])), c2, nmc2);
+          s[2 * q] = __float_as_uint(x.x);
+          s[2 * q + 1] = __float_as_uint(x.y);
+        }
       };
       auto pair_exp = [&](int q) {
-        constexpr int every = kBounded ? kPolyEveryBounded : kPolyEvery;
-        if (every > 0 && (q % (every > 0 ? every : 1)) == (every - 1)) {
-          // every kPolyEvery-th pair is exponentiated on the FMA pipe: the special-function unit delivers only
-          // 16 results per clock and SM, half of what the tensor core consumes at head_dim 64
-          const float2 e = exp2_poly2(make_float2(__uint_as_float(s[2 * q]), __uint_as_float(s[2 * q + 1])));
+        // some pairs are exponentiated on the FMA pipe: the special-function unit delivers only 16 results per
+        // clock and SM, half of what the tensor core consumes at head_dim 64
+        const bool poly = kBounded ? ((q + 1) * kBoundedPolyNum) / kBoundedPolyDen != (q * kBoundedPolyNum) / kBoundedPolyDen
+                                   : (kPolyEvery > 0 && (q % (kPolyEvery > 0 ? kPolyEvery : 1)) == (kPolyEvery - 1));
+        if (poly) {
+          const float2 x = make_float2(__uint_as_float(s[2 * q]), __uint_as_float(s[2 * q + 1]));
+          float2 e;
+          if constexpr (kBounded) e = exp2_poly2_inrange<kBoundedPolyDeg>(x, kBoundedFold ? 0.f : ref_fixed);   // exponents lie in [-126, 1]
+          else e = exp2_poly2(x);
           s[2 * q] = __float_as_uint(e.x);
           s[2 * q + 1] = __float_as_uint(e.y);
+        } else if constexpr (kBounded && !kBoundedFold) {
+          const float2 y = __fadd2_rn(make_float2(__uint_as_float(s[2 * q]), __uint_as_float(s[2 * q + 1])),
+                                      make_float2(-ref_fixed, -ref_fixed));
+          s[2 * q] = __float_as_uint(fast_exp2(y.x));
+          s[2 * q + 1] = __float_as_uint(fast_exp2(y.y));
         } else {
           s[2 * q] = __float_as_uint(fast_exp2(__uint_as_float(s[2 * q])));
           s[2 * q + 1] = __float_as_uint(fast_exp2(__uint_as_float(s[2 * q + 1])));
@@ -614,9 +863,9 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int q = 0; q < kFfmaAhead; ++q) pair_ffma(q);
 #pragma unroll
       for (int q = 0; q < 64; ++q) {
-        if constexpr (kBounded && kBoundedOverlap) {
+        if constexpr (kBounded) {
           // bounded mode needs no row maximum: the second half of the S row arrives under the first half of the sweep
-          if (q == 32 - kFfmaAhead) {
+          if (kBoundedHalfAt > 0 && q == kBoundedHalfAt) {
             tmem_wait_ld();
             tc_fence_before();
             __syncwarp();
@@ -624,7 +873,7 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (valid < 128) {
 #pragma unroll
               for (int i = 64; i < 128; ++i)
-                if (i >= valid) s[i] = 0xff800000u;
+                if (i >= valid) s[i] = kMaskBits;
             }
           }
         }
@@ -644,7 +893,7 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_st32(p_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[kPvWaitAt > 31 ? 32 : 0]));
       const float rs0 = acc0.x, rs1 = acc0.y, rs2 = acc1.x, rs3 = acc1.y;
       l = fmaf(l, alpha, (rs0 + rs1) + (rs2 + rs3));
-      if (j + 1 == nblk) {                          // otherwise the next iteration announces P after its first loads
+      if (j + 1 == nblk || (kBounded && kEarlyPFull)) {   // otherwise the next iteration announces P after its first loads
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
@@ -653,7 +902,7 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
 
     // ---- epilogue: O / l ----
-    if (ok && nblk > 0) ok = mbar_wait(bar_pv_full(t), (nblk - 1) & 1, cta_abort, a.status);
+    if (ok && nblk > 0) ok = wait_v(bar_pv_full(t), (nblk - 1) & 1);
     const int qrow = (qg * QT + t) * kTileM + row;
     if (ok && nblk > 0) {
       tc_fence_after();
@@ -687,7 +936,7 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
       if (qrow < a.n_q && !a.final_bf16)
-        a.part_lse[prow] = ((kBounded ? ref_fixed : m * c) + log2f(l)) * 0.6931471805599453f;
+        a.part_lse[prow] = (((kBounded && !running_max) ? ref_fixed : m * c) + log2f(l)) * 0.6931471805599453f;
     }
   }
 
@@ -709,6 +958,29 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 int attention_smem_bytes(int qt) {
   return static_cast<int>((qt == 2 ? SmemLayout<2>::total : SmemLayout<1>::total) + 1024);
 }
+
+// The kernels need more dynamic shared memory than the default limit; the opt-in is a per-device attribute of each
+// kernel, so it is recorded per device ordinal.
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_attr_mutex;
+bool g_attr_set[kMaxDevices] = {false};
+
+int opt_in_shared_memory() {
+  int dev = -1;
+  GCT_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(GCT_ERR_INVALID, "attention: device ordinal out of range");
+  std::lock_guard<std::mutex> lock(g_attr_mutex);
+  if (!g_attr_set[dev]) {
+    const int s2 = attention_smem_bytes(2), s1 = attention_smem_bytes(1);
+    GCT_CUDA_CHECK(cudaFuncSetAttribute(gct_attn_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, s2));
+    GCT_CUDA_CHECK(cudaFuncSetAttribute(gct_attn_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, s2));
+    GCT_CUDA_CHECK(cudaFuncSetAttribute(gct_attn_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, s1));
+    g_attr_set[dev] = true;
+  }
+  return GCT_OK;
+}
+}  // namespace
 
 int launch_attention(const AttnLaunch& a, cudaStream_t stream) {
   if (a.n_q <= 0 || a.heads <= 0 || a.batch <= 0 || a.n_pages <= 0 || a.page_len <= 0 || a.last_page_len <= 0 ||
@@ -735,12 +1007,11 @@ int launch_attention(const AttnLaunch& a, cudaStream_t stream) {
   k.part_o = a.part_o;
   k.part_lse = a.part_lse;
   k.status = a.status;
-  k.row_ref = a.row_ref;
-  k.unsafe_epoch = a.unsafe_epoch;
-  k.epoch = a.epoch;
-  const bool bounded = a.unsafe_epoch != nullptr;
-  if (bounded && (a.row_ref == nullptr || a.q_tiles_per_cta != 2))
-    return fail(GCT_ERR_INVALID, "attention: bounded mode needs row references and two query tiles per CTA");
+  k.key_norm_max = a.key_norm_max;
+  k.bounded_limit = a.bounded_limit;
+  const bool bounded = a.key_norm_max != nullptr;
+  if (bounded && (a.q_tiles_per_cta != 2 || !(a.bounded_limit > 0.f)))
+    return fail(GCT_ERR_INVALID, "attention: bounded mode needs two query tiles per CTA and a positive limit");
   if (a.splits < 1 || a.splits > k.total_blocks) return fail(GCT_ERR_INVALID, "attention: splits out of range");
   if (a.final_bf16 && (a.splits != 1 || a.out == nullptr)) return fail(GCT_ERR_INVALID, "attention: final output needs splits == 1");
   if (!a.final_bf16 && (a.part_o == nullptr || a.part_lse == nullptr))
@@ -748,23 +1019,14 @@ int launch_attention(const AttnLaunch& a, cudaStream_t stream) {
   const long long grid = static_cast<long long>(k.q_groups) * a.splits * a.heads * a.batch;
   if (grid <= 0 || grid > 0x7fffffffLL) return fail(GCT_ERR_INVALID, "attention: grid too large");
   const int smem = attention_smem_bytes(a.q_tiles_per_cta);
+  int rc = opt_in_shared_memory();
+  if (rc != GCT_OK) return rc;
   if (a.q_tiles_per_cta == 2) {
-    static bool attr_set = false;
-    if (!attr_set) {
-      GCT_CUDA_CHECK(cudaFuncSetAttribute(gct_attn_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      GCT_CUDA_CHECK(cudaFuncSetAttribute(gct_attn_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      attr_set = true;
-    }
-    // bounded mode: both instantiations are launched; each CTA of the one that does not apply returns at once
     if (bounded)
       gct_attn_kernel<2, true><<<static_cast<unsigned>(grid), kThreads<2>, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
-    gct_attn_kernel<2, false><<<static_cast<unsigned>(grid), kThreads<2>, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
+    else
+      gct_attn_kernel<2, false><<<static_cast<unsigned>(grid), kThreads<2>, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
   } else {
-    static bool attr_set = false;
-    if (!attr_set) {
-      GCT_CUDA_CHECK(cudaFuncSetAttribute(gct_attn_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      attr_set = true;
-    }
     gct_attn_kernel<1, false><<<static_cast<unsigned>(grid), kThreads<1>, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
   }
   GCT_CUDA_CHECK(cudaGetLastError());

@@ -51,11 +51,11 @@ struct AttnLaunch {
   float* part_o = nullptr;           // [splits, batch, n_q, H, 64] normalised partial outputs
   float* part_lse = nullptr;         // [splits, batch, n_q, H] natural log-sum-exp
   int* status = nullptr;             // device status word
-  // bounded mode (two query tiles per CTA only): per-row upper bounds of the scaled logits from
-  // launch_row_ref, and the word it sets to `epoch` when some bound is too loose to be used
-  const float* row_ref = nullptr;    // [batch, n_q, H]
-  const int* unsafe_epoch = nullptr;
-  int epoch = 0;
+  // bounded mode (two query tiles per CTA only): key_norm_max[h] bounds the 2-norm of every key of head h that the
+  // page table reaches; a CTA uses |q_row| * key_norm_max[h] * scale * log2(e) as the fixed softmax reference of
+  // its rows while that stays within bounded_limit, otherwise it tracks the running row maximum
+  const float* key_norm_max = nullptr;   // [H]; null: no bounded mode
+  float bounded_limit = 0.f;
 };
 int launch_attention(const AttnLaunch& a, cudaStream_t stream);
 int attention_smem_bytes(int q_tiles_per_cta);
@@ -95,10 +95,6 @@ struct PrepLaunch {
 };
 int launch_prep(const PrepLaunch& p, cudaStream_t stream);
 
-// row_ref[row] = |q_row| * key_norm_max[head] * scale * log2(e) for the rows of q [rows/heads, heads, 64] bf16;
-// *unsafe_epoch = epoch when a reference exceeds `limit` (or is not finite).
-int launch_row_ref(const __nv_bfloat16* q, int64_t rows, int heads, const float* key_norm_max, float limit,
-                   float* row_ref, int* unsafe_epoch, int epoch, cudaStream_t stream);
 // key_norm_max[head] = max over all K rows of the pool [pages, 2, page_size, heads, 64] of their 2-norm
 int launch_scan_keys(const __nv_bfloat16* pool, int num_pages, int page_size, int heads, float* key_norm_max,
                      cudaStream_t stream);

@@ -239,26 +239,6 @@ gct_merge_kernel(const float* __restrict__ parts, const float* __restrict__ lse,
   if (lse_out != nullptr && lane == 0) lse_out[row] = mx + logf(den);
 }
 
-// One warp per query row: reference = |q| * max|k| of the head * scale * log2(e) >= every scaled logit of the row
-// (Cauchy-Schwarz), usable as a fixed softmax reference while it stays below `limit`.
-__global__ void __launch_bounds__(256)
-gct_row_ref_kernel(const __nv_bfloat16* __restrict__ q, int64_t rows, int heads, const float* __restrict__ key_norm_max,
-                   float limit, float* __restrict__ row_ref, int* unsafe_epoch, int epoch) {
-  const int lane = threadIdx.x & 31;
-  const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  if (row >= rows) return;
-  const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(q + row * kHeadDim + 2 * lane);
-  const float2 f = __bfloat1622float2(v);
-  float sq = f.x * f.x + f.y * f.y;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-  if (lane == 0) {
-    const float ref = sqrtf(sq) * key_norm_max[row % heads] * (0.125f * 1.4426950408889634f);
-    row_ref[row] = ref;
-    if (!(ref <= limit)) atomicExch(unsafe_epoch, epoch);   // too loose, infinite or NaN
-  }
-}
-
 // Eight lanes per K row of the pool (16 bytes each), four rows per warp and load, four loads in flight per lane.
 __global__ void __launch_bounds__(256)
 gct_scan_keys_kernel(const __nv_bfloat16* __restrict__ pool, int64_t total_rows, int page_size, int heads,
@@ -387,16 +367,6 @@ int launch_merge(const float* parts, const float* lse, int groups, int64_t rows,
   const int blocks = static_cast<int>((rows * 32 + 255) / 256);
   gct_merge_kernel<<<blocks, 256, 0, stream>>>(parts, lse, groups, rows, parts_stride, lse_stride, out_bf16, out_f32,
                                                lse_out);
-  GCT_CUDA_CHECK(cudaGetLastError());
-  return GCT_OK;
-}
-
-int launch_row_ref(const __nv_bfloat16* q, int64_t rows, int heads, const float* key_norm_max, float limit,
-                   float* row_ref, int* unsafe_epoch, int epoch, cudaStream_t stream) {
-  if (q == nullptr || key_norm_max == nullptr || row_ref == nullptr || unsafe_epoch == nullptr || rows <= 0 || heads <= 0)
-    return fail(GCT_ERR_INVALID, "row_ref: bad argument");
-  const int blocks = static_cast<int>((rows * 32 + 255) / 256);
-  gct_row_ref_kernel<<<blocks, 256, 0, stream>>>(q, rows, heads, key_norm_max, limit, row_ref, unsafe_epoch, epoch);
   GCT_CUDA_CHECK(cudaGetLastError());
   return GCT_OK;
 }

@@ -54,14 +54,17 @@ int make_tensor_map(CUtensorMap* out, const void* base, int heads, int64_t token
   return GCT_OK;
 }
 
+// SM count of the current device, cached per device ordinal.
 static int device_sm_count(int* out) {
-  static int cached = 0;
-  if (cached == 0) {
-    int dev = 0;
-    GCT_CUDA_CHECK(cudaGetDevice(&dev));
-    GCT_CUDA_CHECK(cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev));
-  }
-  *out = cached;
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static int cached[kMaxDevices] = {0};
+  int dev = 0;
+  GCT_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(GCT_ERR_INVALID, "device ordinal out of range");
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == 0) GCT_CUDA_CHECK(cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev));
+  *out = cached[dev];
   return GCT_OK;
 }
 
@@ -96,11 +99,8 @@ struct gct_mgr {
   float* part_lse = nullptr;
   int max_splits = 0;
   // bounded softmax reference: running max of |k| per (block, head) on the device, kept by every K write that goes
-  // through the manager; per-row references and the "bound too loose" word of the current attention call
+  // through the manager
   float* key_norm_max = nullptr;     // [num_blocks, H] inside the workspace header (null: does not fit)
-  float* row_ref = nullptr;          // [tokens_per_frame, H]
-  int* unsafe_epoch = nullptr;
-  int epoch = 0;
   bool bounded_enabled = true;
   std::vector<char> key_norm_valid, key_norm_clear;
   // plan
@@ -139,17 +139,15 @@ static void reset_block(const gct_mgr* m, BlockState& b) {
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct WsLayout {
-  size_t table_off, qstage_off, rowref_off, parto_off, partlse_off, total_min, per_split;
+  size_t table_off, qstage_off, parto_off, partlse_off, total_min, per_split;
 };
-static constexpr size_t kWsEpochOff = 64;        // "bound too loose" word of the bounded mode
 static constexpr size_t kWsKeyNormOff = 256;     // key_norm_max[num_blocks][H] up to the end of the header
 static WsLayout ws_layout(const gct_mgr* m) {
   WsLayout w;
   const size_t rows = static_cast<size_t>(m->cfg.tokens_per_frame) * m->cfg.num_heads;
   w.table_off = kWsHeader;
   w.qstage_off = align_up(w.table_off + static_cast<size_t>(m->geo.max_num_pages) * 4, 256);
-  w.rowref_off = align_up(w.qstage_off + rows * kHeadDim * 2, 256);
-  w.parto_off = align_up(w.rowref_off + rows * 4, 256);
+  w.parto_off = align_up(w.qstage_off + rows * kHeadDim * 2, 256);
   w.per_split = rows * kHeadDim * 4 + rows * 4;
   w.partlse_off = 0;
   w.total_min = w.parto_off + 2 * w.per_split + 256;
@@ -272,9 +270,6 @@ int gct_mgr_bind(gct_mgr_t* m, void* const* pools_dev, void* workspace_dev, size
   m->part_o = reinterpret_cast<float*>(m->ws + w.parto_off);
   m->part_lse = reinterpret_cast<float*>(m->ws + w.parto_off + static_cast<size_t>(m->max_splits) * rows * kHeadDim * 4);
   GCT_CUDA_CHECK(cudaMemset(m->ws, 0, kWsHeader));
-  m->row_ref = reinterpret_cast<float*>(m->ws + w.rowref_off);
-  m->unsafe_epoch = reinterpret_cast<int*>(m->ws + kWsEpochOff);
-  m->epoch = 0;
   const size_t kn_bytes = static_cast<size_t>(m->cfg.num_blocks) * H * sizeof(float);
   m->key_norm_max = kWsKeyNormOff + kn_bytes <= kWsHeader ? reinterpret_cast<float*>(m->ws + kWsKeyNormOff) : nullptr;
   // nothing is visible yet and the header was just zeroed: a maximum of 0 is exact
@@ -661,19 +656,10 @@ static int run_paged(gct_mgr* m, int block, const void* q_dev, int q_dtype, int 
   choose_attention_config((n_q + kTileM - 1) / kTileM, H, total_blocks, sms, m->max_splits, &a.q_tiles_per_cta, &a.splits);
   const int64_t rows = static_cast<int64_t>(n_q) * H;
   // Bounded mode: every key of this block's cache went through the manager, so |q_row| * max|k| bounds the row's
-  // logits; while that bound stays small it replaces the running row maximum (decided on the device, per call).
+  // logits; while that bound stays small it replaces the running row maximum (decided per CTA inside the kernel).
   if (m->bounded_enabled && m->key_norm_max != nullptr && m->key_norm_valid[block] && a.q_tiles_per_cta == 2) {
-    if (++m->epoch <= 0) {
-      m->epoch = 1;
-      GCT_CUDA_CHECK(cudaMemsetAsync(m->unsafe_epoch, 0, sizeof(int), stream));
-    }
-    rc = launch_row_ref(q, rows, H, m->key_norm_max + static_cast<size_t>(block) * H, kBoundedLimit, m->row_ref,
-                        m->unsafe_epoch, m->epoch, stream);
-    if (rc != GCT_OK) return rc;
-    a.row_ref = m->row_ref;
-    a.unsafe_epoch = m->unsafe_epoch;
-    a.epoch = m->epoch;
-    m->launches += 2;      // the reference kernel and the second attention instantiation
+    a.key_norm_max = m->key_norm_max + static_cast<size_t>(block) * H;
+    a.bounded_limit = kBoundedLimit;
   }
   if (a.splits == 1 && out_bf16 != nullptr && lse_dev == nullptr) {
     a.final_bf16 = true;

@@ -29,7 +29,7 @@ def install(frame_attention: bool = True, patch_embed_attention: bool = None) ->
     if not _saved:
         _saved.update(manager=cache_mod.FlashInferKVCacheManager, block=stream_mod.FlashInferBlock,
                       init=stream_mod.AggregatorStream.__init__)
-    cache_mod.FlashInferKVCacheManager = B200KVCacheManager
+    cache_mod.FlashInferKVCacheManager = _manager_selector(_saved["manager"], B200KVCacheManager)
     stream_mod.FlashInferBlock = B200Block
     if frame_attention:
         cls = stream_mod.AggregatorStream
@@ -42,6 +42,27 @@ def install(frame_attention: bool = True, patch_embed_attention: bool = None) ->
 
             cls.__init__ = wrapped_init
             cls._b200_wrapped = True
+
+
+def _manager_selector(reference_cls, b200_cls):
+    """The class bound to the name `FlashInferKVCacheManager` while the backend is installed.  Constructing it gives
+    a B200KVCacheManager, except with force_fp32=True (lingbot_map/aggregator/stream.py:227-228, set by
+    gct_profile.py:293-296 for --dtype fp32): that is the reference's fp32 gather + SDPA comparison mode
+    (flashinfer_cache.py:372-383), which this backend has no arithmetic for, so the reference's own manager is
+    returned and B200Block runs the reference's block code on it.  isinstance() against the name accepts both."""
+
+    class _Meta(type):
+        def __instancecheck__(cls, obj):
+            return isinstance(obj, (reference_cls, b200_cls))
+
+    class FlashInferKVCacheManager(metaclass=_Meta):
+        def __new__(cls, *args, **kwargs):
+            if kwargs.get("force_fp32", False):
+                return reference_cls(*args, **kwargs)
+            return b200_cls(*args, **kwargs)
+
+    FlashInferKVCacheManager.__doc__ = "selects B200KVCacheManager, or the reference's manager for force_fp32"
+    return FlashInferKVCacheManager
 
 
 def uninstall() -> None:

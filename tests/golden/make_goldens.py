@@ -329,6 +329,76 @@ def model_e2e_values():
     print("  max |paged_kf2 - sdpa_kf1| pose:", float(np.abs(out["paged_kf2_pose_enc"] - out["sdpa_kf1_pose_enc"]).max()))
 
 
+def block_stream_bf16_values():
+    """FlashInferBlock with bf16 weights under bf16 autocast, the way demo.py runs the aggregator (demo.py:458-460,545):
+    the reference's own block code on CPU, `block.to(bfloat16)`, bf16 input, torch.autocast("cpu", bfloat16); the
+    paged manager in its fp32 gather + SDPA mode.  Phase 1 with 2 scale frames, then 5 streaming keyframes."""
+    import torch
+    from lingbot_map.layers.block import FlashInferBlock
+    from lingbot_map.layers.flashinfer_cache import FlashInferKVCacheManager
+    from lingbot_map.layers.rope import WanRotaryPosEmbed, RotaryPositionEmbedding2D
+    dim, H, pph, ppw, ns = 128, 2, 3, 4, 6
+    P = ns + pph * ppw
+    scale, window = 2, 3
+    rope3d = WanRotaryPosEmbed(attention_head_dim=64, patch_size=(1, 14, 14), max_seq_len=64)
+    dev = torch.device("cpu")
+    blk = FlashInferBlock(dim=dim, num_heads=H, init_values=0.01, qk_norm=True,
+                          rope=RotaryPositionEmbedding2D(frequency=100), kv_cache_sliding_window=window,
+                          kv_cache_scale_frames=scale).eval()
+    seeded.fill_module_(blk, 21)
+    blk = blk.to(torch.bfloat16)
+    mgr = FlashInferKVCacheManager(num_blocks=1, max_num_frames=scale + window + 16, tokens_per_frame=P, num_heads=H,
+                                   head_dim=64, dtype=torch.float32, device=dev, scale_frames=scale,
+                                   sliding_window=window, max_total_frames=40, force_fp32=True)
+    kw = dict(num_patches=P - ns, num_special=ns, enable_3d_rope=True, kv_cache=mgr, global_idx=0,
+              num_frame_for_scale=scale, num_register_tokens=4)
+    out = {}
+    with torch.no_grad(), torch.autocast("cpu", dtype=torch.bfloat16):
+        x = torch.from_numpy(seeded.randn(900, 1, scale * P, dim)).to(torch.bfloat16)
+        pos = rope3d(ppf=scale, pph=pph, ppw=ppw, patch_start_idx=ns, device=dev, f_start=0, f_end=scale)
+        y = blk(x, pos=pos, num_frames=scale, num_frame_per_block=scale, **kw)
+        out["phase1"] = y.float().numpy()
+        for i in range(5):
+            x = torch.from_numpy(seeded.randn(901 + i, 1, P, dim)).to(torch.bfloat16)
+            pos = rope3d(ppf=1, pph=pph, ppw=ppw, patch_start_idx=ns, device=dev, f_start=scale + i, f_end=scale + i + 1)
+            y = blk(x, pos=pos, num_frames=1, num_frame_per_block=1, **kw)
+            out[f"frame{i}"] = y.float().numpy()
+    out["visible_end"] = np.array(mgr.build_visible_page_table(0), np.int32)
+    np.savez_compressed(os.path.join(HERE, "block_stream_bf16.npz"), **out)
+    print("block_stream_bf16.npz:", {k: (v.shape, float(np.abs(v).max())) for k, v in out.items()})
+
+
+MODEL_E2E_518 = dict(height=378, width=518, frames=8, num_scale_frames=2, weight_seed=7, image_seed=0, depth_stride=7)
+
+
+def model_e2e_518_images():
+    c = MODEL_E2E_518
+    return np.random.RandomState(c["image_seed"]).rand(c["frames"], 3, c["height"], c["width"]).astype(np.float32)
+
+
+def model_e2e_518_values():
+    """The whole GCTStream model at the production frame size 378x518 (1005 tokens per frame, page of 999 tokens with
+    its 103-token tail block), default cache geometry (8 anchor frames, window 64), 8 frames U[0,1): 2 scale frames
+    in phase 1, then 6 streaming frames, keyframe interval 1; fp32 on CPU through the paged manager's fp32
+    gather + SDPA path.  Stores camera encodings and a strided sample of the depth maps."""
+    import torch
+    from lingbot_map.models.gct_stream import GCTStream
+    c = MODEL_E2E_518
+    model = GCTStream(img_size=518, patch_size=14, enable_3d_rope=True, max_frame_num=64, camera_num_iterations=4,
+                      use_sdpa=False).eval()
+    seeded.fill_model_(model, c["weight_seed"])
+    model.aggregator.kv_cache_force_fp32 = True
+    imgs = torch.from_numpy(model_e2e_518_images())
+    with torch.no_grad():
+        pred = model.inference_streaming(imgs, num_scale_frames=c["num_scale_frames"], keyframe_interval=1)
+    st = c["depth_stride"]
+    out = {"pose_enc": pred["pose_enc"][0].numpy().astype(np.float32),
+           "depth": pred["depth"][0, :, ::st, ::st, 0].numpy().astype(np.float32),
+           "visible_end": np.array(model.aggregator.kv_cache_manager.build_visible_page_table(0), np.int32)}
+    np.savez_compressed(os.path.join(HERE, "model_e2e_518_fp32.npz"), **out)
+    print("model_e2e_518_fp32.npz:", {k: v.shape for k, v in out.items()})
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("LINGBOT_MAP_REFERENCE"), required="LINGBOT_MAP_REFERENCE" not in os.environ,
@@ -337,7 +407,8 @@ if __name__ == "__main__":
     args = ap.parse_args()
     _import_reference(args.reference)
     todo = {"manager_traces": manager_traces, "paged_attention": paged_attention_values,
-            "prepare_qkv": prepare_qkv_values, "block_stream": block_stream_values, "model_e2e": model_e2e_values}
+            "prepare_qkv": prepare_qkv_values, "block_stream": block_stream_values, "model_e2e": model_e2e_values,
+            "block_stream_bf16": block_stream_bf16_values, "model_e2e_518": model_e2e_518_values}
     for name, fn in todo.items():
-        if not args.only or name in args.only.split(","):
+        if (not args.only and name != "model_e2e_518") or name in args.only.split(","):
             fn()

@@ -64,10 +64,69 @@ def test_rebinding_builds_b200_blocks_in_reference_aggregator():
         assert all(isinstance(b.attn, P.B200FrameAttention) for b in agg.frame_blocks)
         assert list(agg.state_dict().keys()) == list(ref.state_dict().keys())
         agg.load_state_dict(ref.state_dict(), strict=True)
-        assert cache_mod.FlashInferKVCacheManager is P.B200KVCacheManager
+        # the name now resolves to a selector: a B200 manager, or the reference's own one for force_fp32
+        sel = cache_mod.FlashInferKVCacheManager
+        m = sel(num_blocks=1, max_num_frames=21, tokens_per_frame=26, num_heads=2, head_dim=64, dtype=torch.bfloat16,
+                device=None, scale_frames=2, sliding_window=3, max_total_frames=40, bookkeeping_only=True)
+        assert type(m) is P.B200KVCacheManager and isinstance(m, sel)
     finally:
         stream_mod.FlashInferBlock, cache_mod.FlashInferKVCacheManager, stream_mod.AggregatorStream.__init__ = saved
         stream_mod.AggregatorStream._b200_wrapped = False
+
+
+def test_manager_selector_hands_fp32_mode_back_to_the_reference_class():
+    """force_fp32=True is the reference's fp32 gather + SDPA comparison mode (flashinfer_cache.py:372-383): the
+    selector bound by install() returns the reference's manager for it, a B200 manager otherwise, and isinstance()
+    against the bound name (attention.py:441-443) accepts both."""
+    class FakeReferenceManager:
+        def __init__(self, *args, **kwargs):
+            self.kwargs = kwargs
+
+    sel = P.select._manager_selector(FakeReferenceManager, P.B200KVCacheManager)
+    kw = dict(num_blocks=1, max_num_frames=21, tokens_per_frame=26, num_heads=2, head_dim=64, dtype=torch.float32,
+              device=None, scale_frames=2, sliding_window=3, max_total_frames=40)
+    ref = sel(force_fp32=True, **kw)
+    assert type(ref) is FakeReferenceManager and ref.kwargs["force_fp32"] is True and isinstance(ref, sel)
+    ours = sel(force_fp32=False, bookkeeping_only=True, **kw)
+    assert type(ours) is P.B200KVCacheManager and isinstance(ours, sel)
+    assert not isinstance(object(), sel)
+    with pytest.raises(NotImplementedError):          # the B200 manager itself still has no fp32 arithmetic
+        P.B200KVCacheManager(force_fp32=True, bookkeeping_only=True, **kw)
+
+
+def test_block_uses_a_rebound_attn_pre():
+    """compile_model rebinds blk.attn_pre on the instance (gct_profile.py:51-56); the streaming forward must then
+    route through it.  Checked on CPU with a stand-in manager that records the calls."""
+    blk = P.B200Block(dim=128, num_heads=2, qk_norm=True, kv_cache_sliding_window=3, kv_cache_scale_frames=2)
+    calls = []
+
+    class Manager(P.B200KVCacheManager):
+        def __init__(self):
+            pass
+
+        def __del__(self):
+            pass
+        _skip_append = False
+
+        def append_frame(self, b, k, v):
+            calls.append(("append", b, tuple(k.shape)))
+
+        def evict_frames(self, **kw):
+            calls.append(("evict", kw["block_idx"], kw["sliding_window"]))
+
+        def compute_attention(self, b, q):
+            calls.append(("attend", b))
+            return torch.zeros(q.shape, dtype=torch.float32)
+
+    def fake_attn_pre(x, pos=None, enable_3d_rope=False):
+        calls.append(("attn_pre",))
+        t = torch.zeros(x.shape[1], 2, 64)
+        return t, t, t
+
+    blk.attn_pre = fake_attn_pre
+    y = blk(torch.zeros(1, 10, 128), pos=None, kv_cache=Manager(), global_idx=3)
+    assert y.shape == (1, 10, 128)
+    assert calls == [("attn_pre",), ("append", 3, (10, 2, 64)), ("evict", 3, 3), ("attend", 3)]
 
 
 def test_custom_operators_are_registered_with_fake_implementations():

@@ -106,29 +106,64 @@ def test_frame_attention_matches_reference():
 
 def test_bf16_autocast_path():
     """demo.py casts the aggregator to bf16 and runs under autocast (demo.py:458-460,545): bf16 weights and
-    activations, bf16 LayerNorm parameters."""
-    dim, H, pph, ppw, ns = 128, 2, 3, 4, 6
+    activations, bf16 LayerNorm parameters.  Golden: the reference's own FlashInferBlock with `.to(bfloat16)` under
+    bf16 autocast on CPU (tests/golden/block_stream_bf16.npz, make_goldens.py block_stream_bf16_values).
+
+    Tolerance.  Both sides return bf16, whose spacing at the outputs' magnitude (up to 5.8 here) is 2^-5 = 3.1e-2
+    for |y| in [4, 8) and 2^-6 for [2, 4); the two runs round every intermediate (LayerNorm output, qkv, attention
+    output, proj, two MLP layers, two residual sums) to bf16 at slightly different values, so final results that
+    differ by one or two output rounding steps are expected: max-abs bound = 2 steps at the largest magnitude
+    = 6.3e-2.  The cosine over the whole output is insensitive to single steps and keeps 0.9999."""
+    z = np.load(os.path.join(G, "block_stream_bf16.npz"))
+    dim, H, pph, ppw, ns, scale, window = 128, 2, 3, 4, 6, 2, 3
     Ptok = ns + pph * ppw
     blk = P.B200Block(dim=dim, num_heads=H, init_values=0.01, qk_norm=True, rope=Rope2dStub(),
-                      kv_cache_sliding_window=3, kv_cache_scale_frames=2).eval().to(DEV)
+                      kv_cache_sliding_window=window, kv_cache_scale_frames=scale).eval().to(DEV)
     seeded.fill_module_(blk, 21)
-    ref = P.B200Block(dim=dim, num_heads=H, init_values=0.01, qk_norm=True, rope=Rope2dStub(),
-                      kv_cache_sliding_window=3, kv_cache_scale_frames=2).eval().to(DEV)
-    seeded.fill_module_(ref, 21)
     blk = blk.to(torch.bfloat16)
-    mk = lambda: P.B200KVCacheManager(1, 21, Ptok, H, 64, device=DEV, scale_frames=2, sliding_window=3,
-                                      max_total_frames=40)
-    m1, m2 = mk(), mk()
-    for i in range(5):
-        x = torch.from_numpy(seeded.randn(900 + i, 1, Ptok, dim)).to(DEV)
+    mgr = P.B200KVCacheManager(1, scale + window + 16, Ptok, H, 64, device=DEV, scale_frames=scale,
+                               sliding_window=window, max_total_frames=40)
+    kw = dict(num_patches=Ptok - ns, num_special=ns, enable_3d_rope=True, kv_cache=mgr, global_idx=0,
+              num_frame_for_scale=scale, num_register_tokens=4)
+    tol = dict(max_abs=6.3e-2, cos=0.9999)
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        x = torch.from_numpy(seeded.randn(900, 1, scale * Ptok, dim)).to(DEV).to(torch.bfloat16)
+        y = blk(x, pos=rope3d_pos(0, scale, pph, ppw, ns), num_frames=scale, num_frame_per_block=scale, **kw)
+        assert y.dtype == torch.bfloat16
+        close(y, z["phase1"], "bf16 phase 1", **tol)
+        for i in range(5):
+            x = torch.from_numpy(seeded.randn(901 + i, 1, Ptok, dim)).to(DEV).to(torch.bfloat16)
+            y = blk(x, pos=rope3d_pos(scale + i, 1, pph, ppw, ns), num_frames=1, num_frame_per_block=1, **kw)
+            assert y.dtype == torch.bfloat16
+            close(y, z[f"frame{i}"], f"bf16 frame {i}", **tol)
+    assert mgr.build_visible_page_table(0) == list(z["visible_end"])
+    assert mgr.device_status() == 0
+
+
+def test_block_with_compiled_style_attn_pre_equals_fused_path():
+    """With blk.attn_pre rebound on the instance (what compile_model does) the streaming forward goes through
+    attn_pre + append_frame instead of the fused append; both write the same pages and give the same output."""
+    dim, H, pph, ppw, ns = 128, 2, 3, 4, 6
+    Ptok = ns + pph * ppw
+    mk_blk = lambda: P.B200Block(dim=dim, num_heads=H, init_values=0.01, qk_norm=True, rope=Rope2dStub(),
+                                 kv_cache_sliding_window=3, kv_cache_scale_frames=2).eval().to(DEV)
+    a, b = mk_blk(), mk_blk()
+    seeded.fill_module_(a, 9)
+    seeded.fill_module_(b, 9)
+    b.attn_pre = b.attn_pre                       # instance attribute, as after `b.attn_pre = torch.compile(b.attn_pre)`
+    mk = lambda: P.B200KVCacheManager(1, 21, Ptok, H, 64, device=DEV, scale_frames=2, sliding_window=3, max_total_frames=40)
+    ma, mb = mk(), mk()
+    for i in range(7):
+        skip = i in (3, 5)
+        ma._skip_append = mb._skip_append = skip
+        x = torch.from_numpy(seeded.randn(40 + i, 1, Ptok, dim)).to(DEV)
         pos = rope3d_pos(i, 1, pph, ppw, ns)
         with torch.no_grad():
-            want = ref(x, pos=pos, num_frames=1, enable_3d_rope=True, kv_cache=m2, global_idx=0)
-            with torch.autocast("cuda", dtype=torch.bfloat16):
-                got = blk(x.to(torch.bfloat16), pos=pos, num_frames=1, enable_3d_rope=True, kv_cache=m1, global_idx=0)
-        assert got.dtype == torch.bfloat16
-        close(got, want.double().cpu().numpy(), f"bf16 frame {i}", max_abs=8e-2, cos=0.999)
-    assert m1.build_visible_page_table(0) == m2.build_visible_page_table(0)
+            ya = a(x, pos=pos, num_frames=1, enable_3d_rope=True, kv_cache=ma, global_idx=0)
+            yb = b(x, pos=pos, num_frames=1, enable_3d_rope=True, kv_cache=mb, global_idx=0)
+        assert torch.equal(ya, yb)
+        assert ma.build_visible_page_table(0) == mb.build_visible_page_table(0)
+    assert torch.equal(ma._gather_kv(0)[0], mb._gather_kv(0)[0])
 
 
 def test_plain_attention_without_norm_and_rope():

@@ -89,3 +89,44 @@ def test_patch_embed_attention_converted(model):
     dd = float(np.abs(pred["depth"][0, :, ::st, ::st, 0].float().cpu().numpy() - z["paged_kf1_depth"]).max())
     print(f"patch embed converted: pose max-abs {dp:.3e}, depth max-abs {dd:.3e}")
     assert dp <= 5e-2 and dd <= 5e-2
+
+
+CFG518 = dict(height=378, width=518, frames=8, num_scale_frames=2, weight_seed=7, image_seed=0, depth_stride=7)
+
+
+def test_production_frame_size_378x518():
+    """The reference's CPU-runnable configuration at the production frame size: 378x518 (1005 tokens per frame, pages
+    of 999 tokens whose last 128-token block holds 103), default cache geometry (8 anchor frames, window 64), 8 frames
+    U[0,1), 2 scale frames in phase 1 and 6 streaming frames, keyframe interval 1.  Golden: the reference's fp32 CPU
+    run of the same seeded model (tests/golden/model_e2e_518_fp32.npz).  Same bound as above: 5e-2 max-abs on the
+    camera encodings and on the depth samples."""
+    z = np.load(os.path.join(G, "model_e2e_518_fp32.npz"))
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    from lingbot_map.models.gct_stream import GCTStream
+    c = CFG518
+    P.select.install()
+    try:
+        m = GCTStream(img_size=518, patch_size=14, enable_3d_rope=True, max_frame_num=64, camera_num_iterations=4,
+                      use_sdpa=False).eval()
+        seeded.fill_model_(m, c["weight_seed"])
+        m = m.to("cuda:0")
+        x = np.random.RandomState(c["image_seed"]).rand(c["frames"], 3, c["height"], c["width"]).astype(np.float32)
+        with torch.no_grad():
+            pred = m.inference_streaming(torch.from_numpy(x).to("cuda:0"), num_scale_frames=c["num_scale_frames"],
+                                         keyframe_interval=1)
+        mgr = m.aggregator.kv_cache_manager
+        assert isinstance(mgr, P.B200KVCacheManager) and mgr.tokens_per_frame == 1005 and mgr.page_size == 999
+        assert mgr.build_visible_page_table(0) == list(z["visible_end"])
+        st = c["depth_stride"]
+        pose = pred["pose_enc"][0].float().cpu().numpy()
+        depth = pred["depth"][0, :, ::st, ::st, 0].float().cpu().numpy()
+        dp = float(np.abs(pose - z["pose_enc"]).max())
+        dd = float(np.abs(depth - z["depth"]).max())
+        print(f"378x518: pose max-abs {dp:.3e}, depth max-abs {dd:.3e}")
+        assert np.isfinite(pose).all() and np.isfinite(depth).all()
+        assert dp <= 5e-2, f"camera encoding differs by {dp}"
+        assert dd <= 5e-2, f"depth differs by {dd}"
+        assert mgr.device_status() == 0
+    finally:
+        P.select.uninstall()

@@ -15,6 +15,7 @@ import torch
 
 import lingbot_map_b200 as P
 from lingbot_map_b200 import _lib
+from oracle import gct_oracle as O
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -68,6 +69,49 @@ def test_static_scratch_matches_workspace_path_twice():
     m2 = _static_attention(m, 0, q1[:130].contiguous())
     _compare(m2, m.compute_attention(0, q1[:130].contiguous()), "third call")
     assert m.device_status() == 0
+
+
+def _oracle(m, block, q):
+    kk, vv = m._gather_kv(block)
+    f64 = lambda t: t.float().cpu().numpy().astype(np.float64)
+    return torch.from_numpy(O.attention(f64(q), f64(kk), f64(vv))[0])
+
+
+def test_static_scratch_against_the_oracle_without_allocating():
+    """The entry point against the float64 oracle (not only against the workspace path, which runs the same kernels),
+    in both of its shapes: a KV range split over CTAs (few heads, long KV: partials in the static array, merged),
+    and many heads with a short KV (one pass, bf16 written directly).  No device memory may be allocated by a call:
+    the free memory reported by the driver and torch's allocator statistics are unchanged across the second call."""
+    g = torch.Generator(device=DEV).manual_seed(5)
+    rn = lambda *s: torch.randn(*s, device=DEV, generator=g).to(torch.bfloat16)
+    cases = []
+    for tpf, H, frames in ((306, 2, 30), (134, 16, 3)):
+        m = P.B200KVCacheManager(1, 48, tpf, H, 64, device=DEV, scale_frames=4, sliding_window=28, max_total_frames=200)
+        for _ in range(frames):
+            m.append_frame(0, rn(tpf, H, 64), rn(tpf, H, 64))
+            m.evict_frames(0, 4, 28)
+        cases.append((m, rn(tpf, H, 64)))
+    for i, (m, q) in enumerate(cases):
+        _static_attention(m, 0, q)                     # first call on this device / of this shape
+        torch.cuda.synchronize()
+        lib = _lib.load()
+        vis = m.build_visible_page_table(0)
+        pages = (C.c_int32 * len(vis))(*vis)
+        out = torch.empty_like(q)
+        stats0 = (torch.cuda.memory_allocated(DEV), torch.cuda.memory_reserved(DEV))
+        free0, _ = torch.cuda.mem_get_info(DEV)
+        status = C.c_int(-1)
+        with torch.cuda.device(DEV):
+            _lib.check(lib.gct_attn_paged_static(m.kv_caches[0].data_ptr(), m.max_num_pages, m.page_size, m.num_heads,
+                                                 pages, len(vis), m.compute_last_page_len(0), q.data_ptr(), q.shape[0],
+                                                 out.data_ptr(), torch.cuda.current_stream(DEV).cuda_stream,
+                                                 C.byref(status)))
+        free1, _ = torch.cuda.mem_get_info(DEV)
+        assert status.value == 0
+        assert (torch.cuda.memory_allocated(DEV), torch.cuda.memory_reserved(DEV)) == stats0
+        # the scratch of one call (page table + partials + log-sum-exps) would be megabytes
+        assert free0 - free1 < 256 * 1024, f"device memory shrank by {free0 - free1} bytes across a call"
+        _compare(out, _oracle(m, 0, q), f"case {i} vs oracle")
 
 
 def test_static_scratch_rejects_oversize():
