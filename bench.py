@@ -435,7 +435,7 @@ def run_gpu(args):
         del hps
         torch.cuda.empty_cache()
         sub_args = argparse.Namespace(**vars(args))
-        sub_args.steps, sub_args.warmup, sub_args.e2e_steps = min(args.steps, 40), 3, min(args.e2e_steps, 3)
+        sub_args.steps, sub_args.warmup, sub_args.e2e_steps = min(args.steps, 40), 3, min(args.e2e_steps, 5)
         khps = build(True, 1)
         kpar = kvsplit_parity(khps[0], rank, dev)
         kres = measure(khps, sub_args, dev, rank, world, barrier, None, True)
@@ -773,7 +773,9 @@ def main():
     ap.add_argument("--streams-per-gpu", type=int, default=1,
                     help="independent streams per GPU, interleaved step by step on one CUDA stream")
     ap.add_argument("--frames-cached", type=int, default=10000)
-    ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--e2e-steps", type=int, default=0,
+                    help="timed steps of the end-to-end pass (0: as many as --steps, so that both passes see the same "
+                         "clocks under the power cap)")
     ap.add_argument("--kernel-steps", type=int, default=20,
                     help="steps of the second pass that brackets every attention launch with CUDA events")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -791,6 +793,8 @@ def main():
     ap.add_argument("--layers", type=int, default=24,
                     help="aggregator depth; the metric is defined at 24, smaller values are for profiler captures")
     args = ap.parse_args()
+    if args.e2e_steps <= 0:
+        args.e2e_steps = args.steps
     DEPTH = args.layers
     SCALE_FRAMES, WINDOW = args.scale_frames, args.window
     if args.impl == "reference":

@@ -202,6 +202,38 @@ int gct_lse_merge_strided(const float* parts_dev, const float* lse_dev, int grou
                           int64_t parts_group_stride, int64_t lse_group_stride, void* out_dev, float* lse_out_dev,
                           void* stream);
 
+/* KV-sharded single stream over several GPUs (no counterpart in the reference, which is single-GPU; the result
+ * equals compute_attention, flashinfer_cache.py:385-421, over the union of the ranks' page slices).  Every rank has
+ * planned its own slice of the visible page list (gct_mgr_plan with a sub-range; has_pages = 0 for a rank whose
+ * slice is empty) and calls this once per layer, all ranks in the same order.  The call runs the paged attention
+ * over the slice and then one kernel that (1) stores, for every peer, this rank's partial result of the rows the
+ * peer owns into the peer's receive buffer and raises a flag there, (2) waits for every rank's flag, merges the
+ * partials of its own row slice by their log-sum-exps, rounds to bf16 and stores the rows into every rank's output
+ * buffer, (3) waits until every rank's rows have arrived.  Plain loads and stores on peer-mapped addresses.
+ *   recv_ptrs[r], out_ptrs[r], flag_ptrs[r]: rank r's receive buffer (gct_kv_exchange_sizes bytes), output
+ *   [n_q, H, 64] bf16 and flag words (zeroed once before the first call), as addresses valid on THIS device
+ *   (symmetric / peer-mapped memory; entry `rank` is local memory).  epoch: 1, 2, 3, ... per call on the same flag
+ *   words, identical on every rank.  All waits are bounded; a timeout sets the manager's device status word. */
+int gct_kv_exchange_sizes(int n_q, int heads, int world, size_t* recv_bytes_out, size_t* flag_bytes_out,
+                          int* slice_rows_out);
+int gct_mgr_attention_exchange(gct_mgr_t* m, int block, const void* q_dev, int q_dtype, int n_q, int rank, int world,
+                               int has_pages, void* const* recv_ptrs, void* const* out_ptrs, void* const* flag_ptrs,
+                               int slice_rows, int epoch, void* stream);
+
+/* Append-only cache of ONE token per frame with its attention, for the camera head: CausalAttention's streaming
+ * branch (lingbot_map/layers/attention.py:222-283) as the camera head drives it (lingbot_map/heads/camera_head.py:
+ * 284-358): the dict cache there grows by torch.cat every frame, is cloned and never evicted (attention.py:307).
+ * cache_k_dev / cache_v_dev: [capacity, H, D] fp32 owned by the caller, `cached` rows valid.  The n_new (1..8) new
+ * tokens q/k_new/v_new [n_new, H, D] fp32 attend to the cached rows and to each other (all-true mask,
+ * attention.py:276-283); with store != 0 their K/V rows are appended at row `cached` (the caller then counts them),
+ * with store == 0 they are used for this call only (a non-keyframe, attention.py:243-249).  head_dim 64 or 128,
+ * fp32 arithmetic (the reference runs its heads in fp32).  The workspace (gct_decode_workspace_bytes) holds the
+ * split partials and per-head counters; its first 4*H bytes must be zero before the first call. */
+int gct_decode_workspace_bytes(int heads, int head_dim, size_t* bytes_out);
+int gct_decode_attention(const float* q_dev, const float* k_new_dev, const float* v_new_dev, int n_new,
+                         float* cache_k_dev, float* cache_v_dev, int cached, int capacity, int store, int heads,
+                         int head_dim, float* out_dev, void* workspace_dev, size_t workspace_bytes, void* stream);
+
 /* Paged attention that allocates nothing (this entry point has no counterpart in the reference).
  * For hosts that cannot call cudaMalloc - e.g. a process that gave all device memory to its own pool
  * at start-up, or a loop that cannot afford cudaMalloc's device-wide synchronisation - and therefore

@@ -9,5 +9,7 @@ from .cache import B200KVCacheManager  # noqa: F401
 from . import ops  # noqa: F401
 from .block import B200Attention, B200Block, B200FrameAttention  # noqa: F401
 from . import select  # noqa: F401
+from .camera import B200CausalAttention, DecodeCache  # noqa: F401
 
-__all__ = ["B200KVCacheManager", "B200Attention", "B200Block", "B200FrameAttention", "ops", "select"]
+__all__ = ["B200KVCacheManager", "B200Attention", "B200Block", "B200FrameAttention", "B200CausalAttention",
+           "DecodeCache", "ops", "select"]

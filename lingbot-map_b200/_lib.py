@@ -70,6 +70,11 @@ SIGNATURES = {
     "gct_rope2d_table": (_i, [_i, _i, _i, C.c_float, _vp, _vp]),
     "gct_lse_merge": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "gct_lse_merge_strided": (_i, [_vp, _vp, _i, _i, _i, _i64, _i64, _vp, _vp, _vp]),
+    "gct_kv_exchange_sizes": (_i, [_i, _i, _i, C.POINTER(_sz), C.POINTER(_sz), _pi]),
+    "gct_mgr_attention_exchange": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _i, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
+                                        _i, _i, _vp]),
+    "gct_decode_workspace_bytes": (_i, [_i, _i, C.POINTER(_sz)]),
+    "gct_decode_attention": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _sz, _vp]),
     "gct_attn_paged_static": (_i, [_vp, _i, _i, _i, _pi32, _i, _i, _vp, _i, _vp, _vp, _pi]),
 }
 

@@ -102,6 +102,12 @@ int launch_cast_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream
 // parts_stride / lse_stride: elements between consecutive groups (0 = densely packed).
 int launch_merge(const float* parts, const float* lse, int groups, int64_t rows /* n_q*H */, __nv_bfloat16* out_bf16,
                  float* out_f32, float* lse_out, cudaStream_t stream, int64_t parts_stride = 0, int64_t lse_stride = 0);
+// KV-sharded single stream: two-phase exchange + merge over peer-mapped buffers (gct_exchange.cu).
+// parts/lses: this rank's split partials [S][rows][64], [S][rows] (null: the rank owns no page);
+// recv/out/flag pointers: one per rank, addresses valid on this device.
+int launch_kv_exchange(const float* parts, const float* lses, int splits, int rows, int rank, int world, int epoch,
+                       void* const* recv_ptrs, void* const* out_ptrs, void* const* flag_ptrs, int slice_max, int* status,
+                       cudaStream_t stream);
 int launch_rope3d_table(int f, int pph, int ppw, int ns, float* cs, cudaStream_t stream);
 int launch_rope2d_table(int pph, int ppw, int ns, float base, float* cs, cudaStream_t stream);
 

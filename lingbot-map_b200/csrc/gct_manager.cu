@@ -611,8 +611,10 @@ static int timed_attention(gct_mgr* m, const AttnLaunch& a, cudaStream_t stream)
   return rc;
 }
 
+// splits_out != nullptr: stop after the attention kernel and leave its split partials (part_o, part_lse) in the
+// workspace for the caller; *splits_out receives their count.
 static int run_paged(gct_mgr* m, int block, const void* q_dev, int q_dtype, int n_q, __nv_bfloat16* out_bf16,
-                     float* out_f32, float* lse_dev, cudaStream_t stream) {
+                     float* out_f32, float* lse_dev, cudaStream_t stream, int* splits_out = nullptr) {
   int rc = check_bound(m);
   if (rc != GCT_OK) return rc;
   if (block < 0 || block >= m->cfg.num_blocks) return fail(GCT_ERR_INVALID, "attention: block index out of range");
@@ -661,6 +663,14 @@ static int run_paged(gct_mgr* m, int block, const void* q_dev, int q_dtype, int 
     a.key_norm_max = m->key_norm_max + static_cast<size_t>(block) * H;
     a.bounded_limit = kBoundedLimit;
   }
+  if (splits_out != nullptr) {
+    a.final_bf16 = false;
+    a.part_o = m->part_o;
+    a.part_lse = m->part_lse;
+    *splits_out = a.splits;
+    m->launches += 1;
+    return timed_attention(m, a, stream);
+  }
   if (a.splits == 1 && out_bf16 != nullptr && lse_dev == nullptr) {
     a.final_bf16 = true;
     a.out = out_bf16;
@@ -688,6 +698,37 @@ int gct_mgr_attention_partial(gct_mgr_t* m, int block, const void* q_dev, int q_
                               float* lse_dev, void* stream) {
   if (out_f32_dev == nullptr || lse_dev == nullptr) return fail(GCT_ERR_INVALID, "gct_mgr_attention_partial: null output");
   return run_paged(m, block, q_dev, q_dtype, n_q, nullptr, out_f32_dev, lse_dev, static_cast<cudaStream_t>(stream));
+}
+
+int gct_kv_exchange_sizes(int n_q, int heads, int world, size_t* recv_bytes_out, size_t* flag_bytes_out, int* slice_rows_out) {
+  if (n_q <= 0 || heads <= 0 || world < 1 || world > 16) return fail(GCT_ERR_INVALID, "gct_kv_exchange_sizes: bad argument");
+  const int64_t rows = static_cast<int64_t>(n_q) * heads;
+  const int slice = static_cast<int>((rows + world - 1) / world);
+  if (recv_bytes_out != nullptr) *recv_bytes_out = static_cast<size_t>(world) * slice * (kHeadDim + 1) * sizeof(float);
+  if (flag_bytes_out != nullptr) *flag_bytes_out = static_cast<size_t>(2 * world + 2) * sizeof(int);
+  if (slice_rows_out != nullptr) *slice_rows_out = slice;
+  return GCT_OK;
+}
+
+int gct_mgr_attention_exchange(gct_mgr_t* m, int block, const void* q_dev, int q_dtype, int n_q, int rank, int world,
+                               int has_pages, void* const* recv_ptrs, void* const* out_ptrs, void* const* flag_ptrs,
+                               int slice_rows, int epoch, void* stream) {
+  int rc = check_bound(m);
+  if (rc != GCT_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t rows = static_cast<int64_t>(n_q) * m->cfg.num_heads;
+  if (!has_pages) {
+    m->launches += 1;
+    return launch_kv_exchange(nullptr, nullptr, 0, static_cast<int>(rows), rank, world, epoch, recv_ptrs, out_ptrs, flag_ptrs,
+                              slice_rows, m->status_dev, s);
+  }
+  int splits = 0;
+  rc = run_paged(m, block, q_dev, q_dtype, n_q, nullptr, nullptr, nullptr, s, &splits);
+  if (rc != GCT_OK) return rc;
+  m->launches += 1;
+  // partial rows are laid out with n_q rows per split, which is what the exchange kernel indexes
+  return launch_kv_exchange(m->part_o, m->part_lse, splits, static_cast<int>(rows), rank, world, epoch, recv_ptrs, out_ptrs,
+                            flag_ptrs, slice_rows, m->status_dev, s);
 }
 
 int gct_mgr_device_status(gct_mgr_t* m, void* stream, int* status_out) {

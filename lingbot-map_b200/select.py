@@ -13,14 +13,18 @@ import os
 _saved = {}
 
 
-def install(frame_attention: bool = True, patch_embed_attention: bool = None) -> None:
+def install(frame_attention: bool = True, patch_embed_attention: bool = None, camera_head: bool = None) -> None:
     """Rebind the reference's class names to the B200 implementations.  Call before building GCTStream.
 
     frame_attention: convert the aggregator's per-frame blocks.  patch_embed_attention: also convert the 24
     attention layers of the DINOv2 patch embed (vision_transformer.py:144-171; plain attention over 1004 tokens,
-    no q/k norm, no RoPE); default from LINGBOT_B200_PATCH_EMBED (off unless set to 1)."""
+    no q/k norm, no RoPE); default from LINGBOT_B200_PATCH_EMBED (off unless set to 1).  camera_head: move the
+    camera head's one-token-per-frame dict caches (heads/camera_head.py:284-358) onto the append-only device cache
+    of camera.py; default from LINGBOT_B200_CAMERA_HEAD (on unless set to 0)."""
     if patch_embed_attention is None:
         patch_embed_attention = os.environ.get("LINGBOT_B200_PATCH_EMBED", "0") == "1"
+    if camera_head is None:
+        camera_head = os.environ.get("LINGBOT_B200_CAMERA_HEAD", "1") != "0"
     import lingbot_map.aggregator.stream as stream_mod
     import lingbot_map.layers.flashinfer_cache as cache_mod
     from .block import B200Block
@@ -42,6 +46,20 @@ def install(frame_attention: bool = True, patch_embed_attention: bool = None) ->
 
             cls.__init__ = wrapped_init
             cls._b200_wrapped = True
+    if camera_head:
+        import lingbot_map.heads.camera_head as head_mod
+        hcls = head_mod.CameraCausalHead
+        if not getattr(hcls, "_b200_wrapped", False):
+            _saved.setdefault("head_init", hcls.__init__)
+            head_init = hcls.__init__
+
+            def wrapped_head_init(self, *args, **kwargs):
+                head_init(self, *args, **kwargs)
+                from .camera import convert_camera_head
+                convert_camera_head(self)
+
+            hcls.__init__ = wrapped_head_init
+            hcls._b200_wrapped = True
 
 
 def _manager_selector(reference_cls, b200_cls):
@@ -75,6 +93,10 @@ def uninstall() -> None:
     stream_mod.FlashInferBlock = _saved["block"]
     stream_mod.AggregatorStream.__init__ = _saved["init"]
     stream_mod.AggregatorStream._b200_wrapped = False
+    if "head_init" in _saved:
+        import lingbot_map.heads.camera_head as head_mod
+        head_mod.CameraCausalHead.__init__ = _saved["head_init"]
+        head_mod.CameraCausalHead._b200_wrapped = False
     _saved.clear()
 
 

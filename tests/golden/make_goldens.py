@@ -399,6 +399,32 @@ def model_e2e_518_values():
     print("model_e2e_518_fp32.npz:", {k: v.shape for k, v in out.items()})
 
 
+def camera_head_values():
+    """CameraCausalHead (heads/camera_head.py:157-358) in streaming mode on CPU, fp32: 2 heads of 128 (dim 256),
+    4 refinement iterations x 4 blocks with 3-D RoPE; first call with 3 scale frames at once, then 7 single frames of
+    which two are non-keyframes (_skip_append: attend, do not store).  Stores every call's final pose encoding."""
+    import torch
+    from lingbot_map.heads.camera_head import CameraCausalHead
+    head = CameraCausalHead(dim_in=256, num_heads=2, trunk_depth=4, num_iterations=4, enable_3d_rope=True,
+                            max_frame_num=64).eval()
+    seeded.fill_model_(head, 13)
+    out = {}
+    with torch.no_grad():
+        x = torch.from_numpy(seeded.randn(700, 1, 3, 1, 256))
+        y = head([x], causal_inference=True, num_frame_per_block=3, num_frame_for_scale=3)
+        out["scale"] = y[-1].numpy()
+        for i in range(7):
+            skip = i in (2, 5)
+            for d in head.kv_cache:
+                d["_skip_append"] = skip
+            x = torch.from_numpy(seeded.randn(701 + i, 1, 1, 1, 256))
+            y = head([x], causal_inference=True, num_frame_per_block=1, num_frame_for_scale=3)
+            out[f"frame{i}"] = y[-1].numpy()
+    out["cached_frames"] = np.array([head.kv_cache[0]["k_0"].shape[2]], np.int32)
+    np.savez_compressed(os.path.join(HERE, "camera_head_fp32.npz"), **out)
+    print("camera_head_fp32.npz:", {k: v.shape for k, v in out.items()}, "cached", out["cached_frames"])
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("LINGBOT_MAP_REFERENCE"), required="LINGBOT_MAP_REFERENCE" not in os.environ,
@@ -408,7 +434,8 @@ if __name__ == "__main__":
     _import_reference(args.reference)
     todo = {"manager_traces": manager_traces, "paged_attention": paged_attention_values,
             "prepare_qkv": prepare_qkv_values, "block_stream": block_stream_values, "model_e2e": model_e2e_values,
-            "block_stream_bf16": block_stream_bf16_values, "model_e2e_518": model_e2e_518_values}
+            "block_stream_bf16": block_stream_bf16_values, "model_e2e_518": model_e2e_518_values,
+            "camera_head": camera_head_values}
     for name, fn in todo.items():
         if (not args.only and name != "model_e2e_518") or name in args.only.split(","):
             fn()

@@ -45,6 +45,9 @@ def _worker(rank, world, port, n_pages, page, last_len, ret):
         merged = D.merge_records_reference(rec, n_q, H).numpy()
         full, _ = O.attention(q, k, v)
         err = float(np.abs(merged - full).max())
+        # the two-phase peer exchange (rows owned in slices: partials to the owner, merged slices to everybody)
+        two_phase = D.exchange_host_model(local, n_q, H, rank, world).numpy()
+        err = max(err, float(np.abs(two_phase - full).max()))
         # every rank must hold the same records
         chk = rec.double().sum().reshape(1)
         lst = [torch.zeros(1, dtype=torch.float64) for _ in range(world)]
@@ -81,3 +84,10 @@ def test_shard_page_range_properties():
             assert max(sizes) - min(sizes) <= 1
     with pytest.raises(ValueError):
         D.shard_page_range(4, 2, 2)
+    # row slices of the peer exchange: contiguous, complete, balanced, and never larger than the receive slots
+    for rows in (1, 7, 1005 * 16, 37 * 3):
+        for w in (1, 2, 3, 8):
+            spans = [D.row_slice(rows, r, w) for r in range(w)]
+            assert spans[0][0] == 0 and spans[-1][1] == rows
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            assert max(hi - lo for lo, hi in spans) <= (rows + w - 1) // w

@@ -553,9 +553,15 @@ def test_headline_kv_every_row_of_two_heads(headline_cache, mode):
         out, lse = m.compute_attention(0, q, return_lse=True)
     finally:
         m.set_bounded_mode(True)
+    # Log-sum-exp: with the running maximum the logits are exact products of the bf16 inputs (2e-3 leaves room for
+    # the exponential approximations).  With the folded reference the Q tile is multiplied by scale * log2(e) BEFORE
+    # it is rounded to bf16 for the tensor core (relative 2^-9 per element, the same perturbation for every key of a
+    # row), which moves the logits of a row, and so its log-sum-exp, by up to |logit| * 2^-9 ~ 2e-3 at the logits of
+    # this test (up to ~6 in natural units, measured 2.1e-3); the normalised output does not see a common shift.
+    lse_tol = 2e-3 if mode == "exact" else 4e-3
     for h, (wo, wl) in want.items():
         assert_close(out[:, h:h + 1], wo, f"kv=131928 {mode} head {h}")
-        assert np.abs(lse[:, h].cpu().numpy() - wl[:, 0]).max() < 2e-3
+        assert np.abs(lse[:, h].cpu().numpy() - wl[:, 0]).max() < lse_tol
     assert m.device_status() == 0
 
 
@@ -604,3 +610,39 @@ def test_rows_past_the_valid_length_of_the_last_page_do_not_leak():
         m.set_bounded_mode(bounded)
         assert_close(m.compute_attention(0, bf(q)), want, f"garbage tail, bounded={bounded}")
     assert m.device_status() == 0
+
+
+def test_exchange_kernel_with_one_rank_equals_single_pass():
+    """gct_mgr_attention_exchange with world = 1: the rank's own buffers stand for the peer-mapped ones, so both
+    phases of the exchange kernel (partials -> receive slots, merge of the row slice -> output) run on one GPU
+    without any peer.  Twice on the same flag words (epochs 1, 2), with a split KV range and with a single pass."""
+    import ctypes as C
+    from lingbot_map_b200.cache import _stream_ptr
+    lib = _lib.load()
+    for tpf, H, frames in ((306, 2, 30), (134, 16, 3)):
+        m = P.B200KVCacheManager(1, 48, tpf, H, 64, device=DEV, scale_frames=4, sliding_window=28, max_total_frames=200)
+        orc = O.PagedCacheOracle(1, tpf, H, 64, scale_frames=4, sliding_window=28, max_total_frames=200)
+        for t in range(frames):
+            k, v = seeded.randn(50 + t, tpf, H, 64), seeded.randn(150 + t, tpf, H, 64)
+            m.append_frame(0, bf(k), bf(v))
+            m.evict_frames(0, 4, 28)
+            orc.append_frame(0, r(k), r(v))
+            orc.evict_frames(0, 4, 28)
+        rb, fb, sl = C.c_size_t(), C.c_size_t(), C.c_int()
+        _lib.check(lib.gct_kv_exchange_sizes(tpf, H, 1, C.byref(rb), C.byref(fb), C.byref(sl)))
+        assert sl.value == tpf * H
+        recv = torch.zeros(rb.value // 4, dtype=torch.float32, device=DEV)
+        flags = torch.zeros(64, dtype=torch.int32, device=DEV)
+        out = torch.empty(tpf, H, 64, dtype=torch.bfloat16, device=DEV)
+        one = lambda t: (C.c_void_p * 1)(t.data_ptr())
+        m.plan()
+        kk, vv = orc.gather_kv(0)
+        for epoch in (1, 2):
+            q = seeded.randn(600 + epoch, tpf, H, 64)
+            qd = bf(q)
+            out.zero_()
+            _lib.check(lib.gct_mgr_attention_exchange(m._handle, 0, qd.data_ptr(), _lib.BF16, tpf, 0, 1, 1, one(recv),
+                                                      one(out), one(flags), sl.value, epoch, _stream_ptr(m.device)))
+            assert_close(out, O.attention(r(q), kk, vv)[0], f"exchange world=1 epoch {epoch} ({tpf}x{H})")
+            assert flags[:2].tolist() == [epoch, epoch] and flags[2:4].tolist() == [0, 0]
+        assert m.device_status() == 0
