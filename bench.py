@@ -166,11 +166,13 @@ def bind_to_gpu_numa_node(device_index):
 class HotPath:
     """State of one stream on one GPU: cache manager at the n_cached-frame steady state + synthetic inputs."""
 
-    def __init__(self, device, n_cached, extra_frames, seed, shard=None):
+    def __init__(self, device, n_cached, extra_frames, seed, shard=None, keyframe_interval=1):
         import lingbot_map_b200 as P
         from lingbot_map_b200 import _lib
         self.P, self.lib, self.dev = P, _lib, device
         self.shard = shard                      # (rank, world) for kvsplit, else None
+        self.kf_interval = max(int(keyframe_interval), 1)
+        self.step_index = 0
         g = torch.Generator(device=device).manual_seed(seed)
         self.mgr = P.B200KVCacheManager(DEPTH, SCALE_FRAMES + WINDOW + 16, TPF, HEADS, HEAD_DIM, device=device,
                                         scale_frames=SCALE_FRAMES, sliding_window=WINDOW,
@@ -201,13 +203,18 @@ class HotPath:
         # 3-D RoPE table of this frame; the reference keeps time indices below max_frame_num, so wrap
         P.ops.rope3d_table(self.frame_index % 1024, PPH, PPW, NSPECIAL, self.dev, out=self.cs3d)
         self.launches += 1
+        # keyframe gate (gct_stream.py:450-464): every kf_interval-th frame stays in the cache; the others are
+        # appended with eviction deferred, attended over and rolled back (block.py:256-263)
+        keyframe = self.step_index % self.kf_interval == 0
+        if not keyframe:
+            m._defer_eviction = True
         for b in range(DEPTH):
             if before_layer is not None:
                 before_layer(b)
             q, k, v = P.ops.prep_qkv(qkv_frame[b], HEADS, TPF, *self.norm[2 * b], self.cs2d, lib.ROPE_2D)
             self.outs[2 * b] = P.ops.dense_attention(q[None], k[None], v[None])
             qg = m.append_frame_fused(b, qkv_global[b], *self.norm[2 * b + 1], self.cs3d, lib.ROPE_3D)
-            m.evict_frames(b, SCALE_FRAMES, WINDOW)
+            m.evict_frames(b, SCALE_FRAMES, WINDOW)      # no-op while deferred
             if self.keep_q is not None:
                 self.keep_q.append(qg)
             if self.shard is None:
@@ -217,9 +224,15 @@ class HotPath:
                 from lingbot_map_b200 import distributed as D
                 self.outs[2 * b + 1] = D.sharded_attention(m, b, qg, *self.shard)
                 self.launches += 5          # prep, dense attention, fused append, paged attention, exchange+merge
+            if not keyframe:
+                m.rollback_last_frame(b)
             if after_layer is not None:
                 after_layer(b)
-        self.frame_index += 1
+        if not keyframe:
+            m._defer_eviction = False
+        else:
+            self.frame_index += 1               # a non-keyframe reuses the time index of the next keyframe
+        self.step_index += 1
 
 
 def _cos64(a, b):
@@ -416,7 +429,8 @@ def run_gpu(args):
         hps = []
         for s in range(n_streams):
             seed = 100 + (0 if kvsplit else rank * n_streams + s)
-            hp = HotPath(dev, args.frames_cached, extra, seed=seed, shard=(rank, world) if kvsplit else None)
+            hp = HotPath(dev, args.frames_cached, extra, seed=seed, shard=(rank, world) if kvsplit else None,
+                         keyframe_interval=args.keyframe_interval)
             if args.exact_softmax:
                 hp.mgr.set_bounded_mode(False)
             hps.append(hp)
@@ -458,7 +472,7 @@ def run_gpu(args):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"GCT hot path, {DEPTH} layers x (frame attention 1005x1005 + fused K/V append + "
                                    f"paged global attention), 518x378, {n_cached_now} cached frames, kv={kv_now} tokens, "
-                                   f"page 999, scale {SCALE_FRAMES} + window {WINDOW}, keyframe_interval 1",
+                                   f"page 999, scale {SCALE_FRAMES} + window {WINDOW}, keyframe_interval {args.keyframe_interval}",
                        "parallelism": ("kv-pages sharded over %d GPUs, peer exchange + LSE merge" % world) if headline_kvsplit
                        else ("%d independent stream(s), %d per GPU" % (res["streams"], args.streams_per_gpu)),
                        "l2": (f"inputs larger than L2 (each layer streams {kv_now * 4096 / 1e6:.0f} MB of K/V)"
@@ -773,6 +787,9 @@ def main():
     ap.add_argument("--streams-per-gpu", type=int, default=1,
                     help="independent streams per GPU, interleaved step by step on one CUDA stream")
     ap.add_argument("--frames-cached", type=int, default=10000)
+    ap.add_argument("--keyframe-interval", type=int, default=1,
+                    help="every K-th streamed frame is a keyframe; the others are appended, attended over and rolled "
+                         "back (the 10,000-frame / interval-5 configuration holds 2,007 keyframes: --frames-cached 2007)")
     ap.add_argument("--e2e-steps", type=int, default=0,
                     help="timed steps of the end-to-end pass (0: as many as --steps, so that both passes see the same "
                          "clocks under the power cap)")

@@ -234,6 +234,23 @@ int gct_decode_attention(const float* q_dev, const float* k_new_dev, const float
                          float* cache_k_dev, float* cache_v_dev, int cached, int capacity, int store, int heads,
                          int head_dim, float* out_dev, void* workspace_dev, size_t workspace_bytes, void* stream);
 
+/* ---- point-cloud helpers of the offline renderer (compute only) ---------------------------- */
+
+/* frustum_cull (demo_render/render_cuda_ext/frustum_cull/frustum_cull.cu:5-53): visible[i] = point i, moved to the
+ * camera frame p = R_cw x + t_cw, lies strictly between the near and far plane and projects into the W x H image.
+ * pts_dev [n, 3] fp32 (16-byte aligned), R_cw / t_cw on the HOST (row-major 3x3, 3), visible_dev [n] bytes (0/1).
+ * Single rounded float operations, no fused multiply-add: a float32 CPU restatement gives the same bits; the
+ * reference's build may contract a*b+c and can differ for points within one rounding step of an image border. */
+int gct_frustum_cull(const float* pts_dev, int64_t n, const float R_cw[9], const float t_cw[3], float fx, float fy,
+                     float cx, float cy, int width, int height, float near_plane, float far_plane, uint8_t* visible_dev,
+                     void* stream);
+/* compute_morton_kernel (demo_render/render_cuda_ext/voxel_morton/voxel_morton.cu:5-47): voxel index
+ * floor(p / voxel_size) per axis, 63-bit Morton code of the indices offset by 2^20, voxel centre, colour copy. */
+int gct_voxel_morton(const float* xyz_dev, const float* rgb_dev, float voxel_size, int64_t n, int64_t* codes_dev,
+                     float* centers_dev, float* colors_dev, void* stream);
+/* mark_unique_kernel (voxel_morton.cu:49-62): mask[i] = i == 0 or sorted[i] != sorted[i-1]. */
+int gct_mark_unique(const int64_t* sorted_dev, int64_t n, uint8_t* mask_dev, void* stream);
+
 /* Paged attention that allocates nothing (this entry point has no counterpart in the reference).
  * For hosts that cannot call cudaMalloc - e.g. a process that gave all device memory to its own pool
  * at start-up, or a loop that cannot afford cudaMalloc's device-wide synchronisation - and therefore

@@ -75,6 +75,10 @@ SIGNATURES = {
                                         _i, _i, _vp]),
     "gct_decode_workspace_bytes": (_i, [_i, _i, C.POINTER(_sz)]),
     "gct_decode_attention": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _sz, _vp]),
+    "gct_frustum_cull": (_i, [_vp, _i64, C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_float, C.c_float, C.c_float,
+                              C.c_float, _i, _i, C.c_float, C.c_float, _vp, _vp]),
+    "gct_voxel_morton": (_i, [_vp, _vp, C.c_float, _i64, _vp, _vp, _vp, _vp]),
+    "gct_mark_unique": (_i, [_vp, _i64, _vp, _vp]),
     "gct_attn_paged_static": (_i, [_vp, _i, _i, _i, _pi32, _i, _i, _vp, _i, _vp, _vp, _pi]),
 }
 

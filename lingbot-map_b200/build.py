@@ -6,7 +6,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = ["csrc/gct_attn_sm100.cu", "csrc/gct_elementwise.cu", "csrc/gct_manager.cu", "csrc/gct_static_scratch.cu",
-           "csrc/gct_exchange.cu", "csrc/gct_decode.cu"]
+           "csrc/gct_exchange.cu", "csrc/gct_decode.cu", "csrc/gct_render.cu"]
 HEADERS = ["csrc/gct_common.h", "../include/gct_b200.h"]
 LIB = os.path.join(HERE, "libgct_b200.so")
 

@@ -103,9 +103,15 @@ struct gct_mgr {
   float* key_norm_max = nullptr;     // [num_blocks, H] inside the workspace header (null: does not fit)
   bool bounded_enabled = true;
   std::vector<char> key_norm_valid, key_norm_clear;
-  // plan
+  // plan: the page table is staged through a small ring of pinned host slots so that its upload is a true
+  // asynchronous copy (a pageable source would be staged by the runtime at call time)
   bool planned = false;
   int plan_pages = 0, plan_last_len = 0;
+  static constexpr int kPlanSlots = 8;
+  int32_t* plan_ring = nullptr;                  // [kPlanSlots][max_num_pages], cudaHostAlloc
+  cudaEvent_t plan_done[kPlanSlots] = {};        // recorded after the copy out of each slot
+  bool plan_used[kPlanSlots] = {};
+  uint64_t plan_count = 0;
   // cached query tensor map
   const void* tmq_ptr = nullptr;
   int tmq_nq = 0;
@@ -190,6 +196,11 @@ int gct_mgr_destroy(gct_mgr_t* m) {
   if (m != nullptr) {
     for (cudaEvent_t e : m->ev_start) cudaEventDestroy(e);
     for (cudaEvent_t e : m->ev_stop) cudaEventDestroy(e);
+    if (m->plan_ring != nullptr) {
+      for (int i = 0; i < gct_mgr::kPlanSlots; ++i)
+        if (m->plan_done[i] != nullptr) cudaEventDestroy(m->plan_done[i]);
+      cudaFreeHost(m->plan_ring);
+    }
   }
   delete m;
   return GCT_OK;
@@ -275,6 +286,13 @@ int gct_mgr_bind(gct_mgr_t* m, void* const* pools_dev, void* workspace_dev, size
   // nothing is visible yet and the header was just zeroed: a maximum of 0 is exact
   m->key_norm_valid.assign(m->cfg.num_blocks, 1);
   m->key_norm_clear.assign(m->cfg.num_blocks, 0);
+  if (m->plan_ring == nullptr) {
+    GCT_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&m->plan_ring),
+                                 static_cast<size_t>(gct_mgr::kPlanSlots) * m->geo.max_num_pages * sizeof(int32_t),
+                                 cudaHostAllocDefault));
+    for (int i = 0; i < gct_mgr::kPlanSlots; ++i)
+      GCT_CUDA_CHECK(cudaEventCreateWithFlags(&m->plan_done[i], cudaEventDisableTiming));
+  }
   m->bound = true;
   m->planned = false;
   m->tmq_ptr = nullptr;
@@ -590,9 +608,15 @@ int gct_mgr_plan(gct_mgr_t* m, int page_begin, int page_end, void* stream) {
   const int last = (page_end == n) ? last_page_len(m, b) : m->geo.page_size;
   if (last < 1 || last > m->geo.page_size)                                                          // :394-396
     return fail(GCT_ERR_INVALID, "block 0: last_page_len=" + std::to_string(last) + " out of range");
-  // pageable source: the runtime stages the bytes before returning, so `vis` may die right after
-  GCT_CUDA_CHECK(cudaMemcpyAsync(m->table_dev, vis.data() + page_begin, static_cast<size_t>(page_end - page_begin) * 4,
+  // pinned staging slot: reused every kPlanSlots plans, after the copy out of it has completed
+  const int slot = static_cast<int>(m->plan_count++ % gct_mgr::kPlanSlots);
+  if (m->plan_used[slot]) GCT_CUDA_CHECK(cudaEventSynchronize(m->plan_done[slot]));
+  int32_t* host = m->plan_ring + static_cast<size_t>(slot) * m->geo.max_num_pages;
+  std::copy(vis.begin() + page_begin, vis.begin() + page_end, host);
+  GCT_CUDA_CHECK(cudaMemcpyAsync(m->table_dev, host, static_cast<size_t>(page_end - page_begin) * 4,
                                  cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+  GCT_CUDA_CHECK(cudaEventRecord(m->plan_done[slot], static_cast<cudaStream_t>(stream)));
+  m->plan_used[slot] = true;
   m->plan_pages = page_end - page_begin;
   m->plan_last_len = last;
   m->planned = true;

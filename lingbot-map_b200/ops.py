@@ -19,12 +19,19 @@ _workspaces = {}
 
 
 def _workspace(device, nbytes: int) -> Tensor:
-    """Per-device scratch (status word + split-KV partials) for calls that have no manager."""
+    """Per-device scratch (status word + split-KV partials) for calls that have no manager.
+
+    One buffer per device, shared by every stream and thread: two dense-attention calls whose GPU work overlaps in
+    time (different streams, or several host threads) race on the split-KV partials and must be serialised by the
+    caller.  When the buffer has to grow, the status word a kernel may have set in the old one is carried over, so
+    device_status() keeps reporting it."""
     key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
+        new = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        if ws is not None:
+            new[:4].copy_(ws[:4])               # stream-ordered after every kernel that used the old buffer
+        _workspaces[key] = ws = new
     return ws
 
 

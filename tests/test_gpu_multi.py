@@ -75,3 +75,31 @@ def test_kv_sharded_attention_matches_single_pass(mode):
         assert worst_abs <= 1e-2 and worst_cos >= 0.99999, f"rank {r}: max_abs={worst_abs:.3e} cosine={worst_cos:.7f}"
         if mode == "peer":
             assert used_peer, "the peer exchange was not set up (symmetric memory unavailable?)"
+
+
+def test_one_process_drives_two_gpus():
+    """The shared-memory opt-in of the attention kernels and the SM count are per-device state: a process that has
+    used GPU 0 must be able to launch the 2-tile kernel (176 KB of dynamic shared memory) on GPU 1 as well.  Small
+    cases only: dense attention with one and two query tiles per CTA, and a paged call through a manager."""
+    import numpy as np
+    sys.path.insert(0, ROOT)
+    import lingbot_map_b200 as P
+    outs = []
+    for dev in ("cuda:0", "cuda:1"):
+        g = torch.Generator().manual_seed(3)                          # host generator: identical inputs on both devices
+        q = torch.randn(1, 300, 4, 64, generator=g).to(dev).to(torch.bfloat16)
+        k = torch.randn(1, 700, 4, 64, generator=g).to(dev).to(torch.bfloat16)
+        small = P.ops.dense_attention(q[:, :100], k, k)               # one tile per CTA
+        big = P.ops.dense_attention(q, k, k)                          # two tiles per CTA
+        ref = torch.nn.functional.scaled_dot_product_attention(q.float().permute(0, 2, 1, 3), k.float().permute(0, 2, 1, 3),
+                                                               k.float().permute(0, 2, 1, 3)).permute(0, 2, 1, 3)
+        assert float((big.float() - ref).abs().max()) < 2e-2 and float((small.float() - ref[:, :100]).abs().max()) < 2e-2
+        m = P.B200KVCacheManager(1, 21, 262, 2, 64, device=dev, scale_frames=2, sliding_window=3, max_total_frames=40)
+        kv = torch.randn(262, 2, 64, generator=g).to(dev)
+        for _ in range(4):
+            m.append_frame(0, kv, kv)
+            m.evict_frames(0, 2, 3)
+        out = m.compute_attention(0, kv.to(torch.bfloat16))
+        assert torch.isfinite(out).all() and m.device_status() == 0 and P.ops.device_status(dev) == 0
+        outs.append(out.cpu())
+    assert torch.equal(outs[0], outs[1])                              # same seeds, same arithmetic on both devices
