@@ -8,7 +8,8 @@
  *     Nothing throws, nothing traps.  gct_last_error() returns a thread-local,
  *     human-readable description of the last failure on the calling thread.
  *   - Pointers named *_dev are device pointers on the current CUDA device; `stream` is a
- *     cudaStream_t passed as void*.  The library never allocates or frees device memory:
+ *     cudaStream_t passed as void*.  A manager belongs to the device that was current at
+ *     gct_mgr_bind: make that device current for every later call on it.  The library never allocates or frees device memory:
  *     page pools, workspace and outputs belong to the caller.
  *   - Token-major "NHD" tensors: [tokens, heads, head_dim] with head_dim == 64.
  *   - dtype codes: GCT_F32 = 0, GCT_BF16 = 1.

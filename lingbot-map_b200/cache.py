@@ -131,8 +131,9 @@ class B200KVCacheManager:
             f"got {k.shape[0] - self.num_special_tokens} (tokens_per_frame={k.shape[0]})")
         k = self._check_frame_tensor(k, "k")
         v = self._check_frame_tensor(v, "v")
-        self._check(self._lib.gct_mgr_append(self._handle, block_idx, k.data_ptr(), _dtype_code(k),
-                                             v.data_ptr(), _dtype_code(v), _stream_ptr(self.device)))
+        with torch.cuda.device(self.device):      # the C ABI works on the current device
+            self._check(self._lib.gct_mgr_append(self._handle, block_idx, k.data_ptr(), _dtype_code(k),
+                                                 v.data_ptr(), _dtype_code(v), _stream_ptr(self.device)))
 
     def append_frame_bookkeeping(self, block_idx: int) -> None:
         """append_frame without device writes (dry runs; KV-sharded replicas that do not own the page).  Whoever
@@ -176,9 +177,10 @@ class B200KVCacheManager:
             q_out = torch.empty(self.tokens_per_frame, self.num_heads, self.head_dim, dtype=torch.bfloat16,
                                 device=self.device)
         ptr = lambda t: None if t is None else t.data_ptr()
-        self._check(self._lib.gct_mgr_append_fused(
-            self._handle, block_idx, qkv.data_ptr(), _dtype_code(qkv), qkv.stride(0), ptr(q_norm_w), ptr(q_norm_b),
-            ptr(k_norm_w), ptr(k_norm_b), ptr(rope_cs), rope_mode, q_out.data_ptr(), _stream_ptr(self.device)))
+        with torch.cuda.device(self.device):
+            self._check(self._lib.gct_mgr_append_fused(
+                self._handle, block_idx, qkv.data_ptr(), _dtype_code(qkv), qkv.stride(0), ptr(q_norm_w), ptr(q_norm_b),
+                ptr(k_norm_w), ptr(k_norm_b), ptr(rope_cs), rope_mode, q_out.data_ptr(), _stream_ptr(self.device)))
         return q_out
 
     def evict_frames(self, block_idx: int, scale_frames: int, sliding_window: int, cross_frame_special: bool = True,
@@ -289,7 +291,8 @@ class B200KVCacheManager:
         """Snapshot block 0's visible page table for the following compute_attention calls
         (the plan() half of flashinfer_cache.py:385-414).  A sub-range selects a KV shard."""
         self._require_device()
-        self._check(self._lib.gct_mgr_plan(self._handle, page_begin, page_end, _stream_ptr(self.device)))
+        with torch.cuda.device(self.device):
+            self._check(self._lib.gct_mgr_plan(self._handle, page_begin, page_end, _stream_ptr(self.device)))
 
     def compute_attention(self, block_idx: int, q: Tensor, return_lse: bool = False):
         """softmax(q k^T / sqrt(D)) v over the visible pages - flashinfer_cache.py:349-421.
@@ -303,9 +306,10 @@ class B200KVCacheManager:
             self.plan()
         out = torch.empty(q.shape, dtype=torch.bfloat16, device=self.device)
         lse = torch.empty(q.shape[0], self.num_heads, dtype=torch.float32, device=self.device) if return_lse else None
-        self._check(self._lib.gct_mgr_attention(self._handle, block_idx, q.data_ptr(), _dtype_code(q), q.shape[0],
-                                                out.data_ptr(), None if lse is None else lse.data_ptr(),
-                                                _stream_ptr(self.device)))
+        with torch.cuda.device(self.device):
+            self._check(self._lib.gct_mgr_attention(self._handle, block_idx, q.data_ptr(), _dtype_code(q), q.shape[0],
+                                                    out.data_ptr(), None if lse is None else lse.data_ptr(),
+                                                    _stream_ptr(self.device)))
         return (out, lse) if return_lse else out
 
     def compute_attention_partial(self, block_idx: int, q: Tensor, out: Optional[Tensor] = None,
@@ -320,27 +324,31 @@ class B200KVCacheManager:
             lse = torch.empty(q.shape[0], self.num_heads, dtype=torch.float32, device=self.device)
         if not (out.is_contiguous() and lse.is_contiguous() and out.dtype == lse.dtype == torch.float32):
             raise ValueError("out and lse must be contiguous float32 tensors")
-        self._check(self._lib.gct_mgr_attention_partial(self._handle, block_idx, q.data_ptr(), _dtype_code(q),
-                                                        q.shape[0], out.data_ptr(), lse.data_ptr(),
-                                                        _stream_ptr(self.device)))
+        with torch.cuda.device(self.device):
+            self._check(self._lib.gct_mgr_attention_partial(self._handle, block_idx, q.data_ptr(), _dtype_code(q),
+                                                            q.shape[0], out.data_ptr(), lse.data_ptr(),
+                                                            _stream_ptr(self.device)))
         return out, lse
 
     def device_status(self) -> int:
         """Synchronises and returns the kernels' status word (0 = ok); raises if a kernel reported a problem."""
         self._require_device()
         st = C.c_int()
-        self._check(self._lib.gct_mgr_device_status(self._handle, _stream_ptr(self.device), C.byref(st)))
+        with torch.cuda.device(self.device):
+            self._check(self._lib.gct_mgr_device_status(self._handle, _stream_ptr(self.device), C.byref(st)))
         return st.value
 
     def kernel_timing(self, max_launches: int) -> None:
         """Time every attention-kernel launch with a CUDA-event pair (0 = off); see kernel_time()."""
         self._require_device()
-        self._check(self._lib.gct_mgr_kernel_timing(self._handle, max_launches))
+        with torch.cuda.device(self.device):
+            self._check(self._lib.gct_mgr_kernel_timing(self._handle, max_launches))
 
     def kernel_time(self):
         """(total milliseconds, launches) of the attention kernel since the last call; synchronises."""
         ms, n = C.c_double(), C.c_int()
-        self._check(self._lib.gct_mgr_kernel_time(self._handle, C.byref(ms), C.byref(n)))
+        with torch.cuda.device(self.device):
+            self._check(self._lib.gct_mgr_kernel_time(self._handle, C.byref(ms), C.byref(n)))
         return ms.value, n.value
 
     @property

@@ -455,6 +455,7 @@ gct_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();      // everything above is private to the CTA; from here on global memory of earlier kernels is read
 
   // QT == 2: 384 threads share 64K registers (168 each at launch); the control warpgroup gives most of its
   // share to the two softmax warpgroups, whose threads hold a whole 128-column S row.
@@ -1021,13 +1022,14 @@ int launch_attention(const AttnLaunch& a, cudaStream_t stream) {
   const int smem = attention_smem_bytes(a.q_tiles_per_cta);
   int rc = opt_in_shared_memory();
   if (rc != GCT_OK) return rc;
+  const dim3 g(static_cast<unsigned>(grid));
   if (a.q_tiles_per_cta == 2) {
     if (bounded)
-      gct_attn_kernel<2, true><<<static_cast<unsigned>(grid), kThreads<2>, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
+      GCT_CUDA_CHECK(launch_pdl(gct_attn_kernel<2, true>, g, dim3(kThreads<2>), smem, stream, a.tm_q, a.tm_k, a.tm_v, k));
     else
-      gct_attn_kernel<2, false><<<static_cast<unsigned>(grid), kThreads<2>, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
+      GCT_CUDA_CHECK(launch_pdl(gct_attn_kernel<2, false>, g, dim3(kThreads<2>), smem, stream, a.tm_q, a.tm_k, a.tm_v, k));
   } else {
-    gct_attn_kernel<1, false><<<static_cast<unsigned>(grid), kThreads<1>, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, k);
+    GCT_CUDA_CHECK(launch_pdl(gct_attn_kernel<1, false>, g, dim3(kThreads<1>), smem, stream, a.tm_q, a.tm_k, a.tm_v, k));
   }
   GCT_CUDA_CHECK(cudaGetLastError());
   return GCT_OK;

@@ -8,6 +8,7 @@
 #include <stdint.h>
 
 #include <string>
+#include <utility>
 
 #include "../../include/gct_b200.h"
 
@@ -23,6 +24,35 @@ int fail(int code, const std::string& msg);
     if (_e != cudaSuccess)                                                                    \
       return ::gct::fail(GCT_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e));   \
   } while (0)
+
+// Programmatic dependent launch between this library's back-to-back kernels of one stream.  A kernel launched
+// through launch_pdl may be scheduled while the last wave of its predecessor is still running; it does its private
+// set-up (barriers, TMEM, descriptor prefetch) and then blocks in pdl_wait() until the predecessor has completed and
+// its memory is visible, so stream order is preserved for every global access.  What is gained is the launch
+// latency and the prologue of every kernel boundary of the five-launch layer loop.
+#ifndef GCT_PDL
+#define GCT_PDL 1
+#endif
+__device__ __forceinline__ void pdl_wait() {
+#if GCT_PDL
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = GCT_PDL ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 constexpr int kHeadDim = 64;
 constexpr int kBlockN = 128;   // KV tokens per attention block (one UMMA N tile)

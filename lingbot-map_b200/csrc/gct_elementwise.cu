@@ -104,6 +104,7 @@ __device__ __forceinline__ void norm_rope8(Row8& x, const float* w, const float*
 }
 
 __global__ void __launch_bounds__(256) gct_prep_kernel(const PrepLaunch p) {
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int part = lane & 7;
   const int wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -217,6 +218,7 @@ __global__ void __launch_bounds__(256)
 gct_merge_kernel(const float* __restrict__ parts, const float* __restrict__ lse, int groups, int64_t rows,
                  int64_t parts_stride, int64_t lse_stride, __nv_bfloat16* __restrict__ out_bf16,
                  float* __restrict__ out_f32, float* __restrict__ lse_out) {
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (row >= rows) return;
@@ -282,6 +284,7 @@ gct_scan_keys_kernel(const __nv_bfloat16* __restrict__ pool, int64_t total_rows,
 // cs[token][m] = (cos, sin) of the m-th complex frequency; fp64 angles as the reference's table
 // (lingbot_map/layers/rope.py:326-334,399-413): m<10 time (dim 20), m<21 height (dim 22), else width (dim 22).
 __global__ void gct_rope3d_table_kernel(int f, int pph, int ppw, int ns, float* cs) {
+  pdl_wait();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   const int tokens = ns + pph * ppw;
   if (idx >= tokens * 32) return;
@@ -344,8 +347,7 @@ int launch_prep(const PrepLaunch& p, cudaStream_t stream) {
   const int head_groups = (p.heads + kHeadsPerWarp - 1) / kHeadsPerWarp;
   const long long warps = static_cast<long long>(p.tokens) * head_groups;
   const int blocks = static_cast<int>((warps * 32 + 255) / 256);
-  gct_prep_kernel<<<blocks, 256, 0, stream>>>(p);
-  GCT_CUDA_CHECK(cudaGetLastError());
+  GCT_CUDA_CHECK(launch_pdl(gct_prep_kernel, dim3(blocks), dim3(256), 0, stream, p));
   return GCT_OK;
 }
 
@@ -365,9 +367,8 @@ int launch_merge(const float* parts, const float* lse, int groups, int64_t rows,
   if (lse_stride <= 0) lse_stride = rows;
   if (parts_stride % 2 != 0) return fail(GCT_ERR_INVALID, "merge: group stride of the partial outputs must be even");
   const int blocks = static_cast<int>((rows * 32 + 255) / 256);
-  gct_merge_kernel<<<blocks, 256, 0, stream>>>(parts, lse, groups, rows, parts_stride, lse_stride, out_bf16, out_f32,
-                                               lse_out);
-  GCT_CUDA_CHECK(cudaGetLastError());
+  GCT_CUDA_CHECK(launch_pdl(gct_merge_kernel, dim3(blocks), dim3(256), 0, stream, parts, lse, groups, rows, parts_stride,
+                            lse_stride, out_bf16, out_f32, lse_out));
   return GCT_OK;
 }
 
@@ -384,8 +385,7 @@ int launch_scan_keys(const __nv_bfloat16* pool, int num_pages, int page_size, in
 
 int launch_rope3d_table(int f, int pph, int ppw, int ns, float* cs, cudaStream_t stream) {
   const int n = (ns + pph * ppw) * 32;
-  gct_rope3d_table_kernel<<<(n + 255) / 256, 256, 0, stream>>>(f, pph, ppw, ns, cs);
-  GCT_CUDA_CHECK(cudaGetLastError());
+  GCT_CUDA_CHECK(launch_pdl(gct_rope3d_table_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, f, pph, ppw, ns, cs));
   return GCT_OK;
 }
 

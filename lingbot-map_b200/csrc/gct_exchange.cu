@@ -69,19 +69,20 @@ __device__ bool wait_flags(const int* f, int world, int epoch, int* status) {
   return true;
 }
 
+// A half-warp per row: 16 lanes x float4 = the 64 output elements; two rows per warp are in flight at once.
 __global__ void __launch_bounds__(256) gct_kv_exchange_kernel(const ExchangeArgs a) {
   __shared__ int s_flag;
-  const int lane = threadIdx.x & 31;
-  const int warps_per_cta = blockDim.x >> 5;
-  const int gwarp = blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
-  const int nwarps = gridDim.x * warps_per_cta;
+  const int lane = threadIdx.x & 15;
+  const int halves_per_cta = blockDim.x >> 4;
+  const int ghalf = blockIdx.x * halves_per_cta + (threadIdx.x >> 4);
+  const int nhalves = gridDim.x * halves_per_cta;
   const int R = a.rows, W = a.world;
   int* my_flags = a.flags[a.rank];
   int* counters = my_flags + 2 * W;
 
   // ---- phase 1: my partial of every row goes to the rank that owns the row ----
-  for (int row = gwarp; row < R; row += nwarps) {
-    float2 acc = make_float2(0.f, 0.f);
+  for (int row = ghalf; row < R; row += nhalves) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float lse = -INFINITY;
     if (a.parts != nullptr) {
       float mx = -INFINITY;
@@ -89,24 +90,29 @@ __global__ void __launch_bounds__(256) gct_kv_exchange_kernel(const ExchangeArgs
       float den = 0.f;
       for (int s = 0; s < a.splits; ++s) {
         const float w = __expf(a.lses[static_cast<size_t>(s) * R + row] - mx);
-        const float2 v = *reinterpret_cast<const float2*>(a.parts + (static_cast<size_t>(s) * R + row) * kHeadDim + 2 * lane);
+        const float4 v = *reinterpret_cast<const float4*>(a.parts + (static_cast<size_t>(s) * R + row) * kHeadDim + 4 * lane);
         acc.x = fmaf(w, v.x, acc.x);
         acc.y = fmaf(w, v.y, acc.y);
+        acc.z = fmaf(w, v.z, acc.z);
+        acc.w = fmaf(w, v.w, acc.w);
         den += w;
       }
       const float inv = 1.f / den;
       acc.x *= inv;
       acc.y *= inv;
+      acc.z *= inv;
+      acc.w *= inv;
       lse = mx + __logf(den);
     }
-    // owner of the row: largest p with p*R/W <= row
+    // owner of the row: the p with p*R/W <= row < (p+1)*R/W
     int p = static_cast<int>((static_cast<long long>(row) * W + W - 1) / R);
+    if (p > W - 1) p = W - 1;
     while (p > 0 && static_cast<long long>(p) * R / W > row) --p;
     while (p + 1 < W && static_cast<long long>(p + 1) * R / W <= row) ++p;
     const int r0 = static_cast<int>(static_cast<long long>(p) * R / W);
     float* rbuf = a.recv[p];
     const size_t slot = static_cast<size_t>(a.rank) * a.slice_max + (row - r0);
-    *reinterpret_cast<float2*>(rbuf + slot * kHeadDim + 2 * lane) = acc;
+    *reinterpret_cast<float4*>(rbuf + slot * kHeadDim + 4 * lane) = acc;
     if (lane == 0) rbuf[static_cast<size_t>(W) * a.slice_max * kHeadDim + slot] = lse;
   }
   __threadfence_system();
@@ -129,22 +135,27 @@ __global__ void __launch_bounds__(256) gct_kv_exchange_kernel(const ExchangeArgs
   const int r1 = static_cast<int>(static_cast<long long>(a.rank + 1) * R / W);
   const float* rbuf = a.recv[a.rank];
   const float* rlse = rbuf + static_cast<size_t>(W) * a.slice_max * kHeadDim;
-  for (int i = gwarp; i < r1 - r0; i += nwarps) {
+  for (int i = ghalf; i < r1 - r0; i += nhalves) {
     float mx = -INFINITY;
-    for (int r = 0; r < W; ++r) mx = fmaxf(mx, rlse[static_cast<size_t>(r) * a.slice_max + i]);
+    for (int r = 0; r < W; ++r) mx = fmaxf(mx, __ldcg(rlse + static_cast<size_t>(r) * a.slice_max + i));
     float den = 0.f;
-    float2 acc = make_float2(0.f, 0.f);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int r = 0; r < W; ++r) {
-      const float w = __expf(rlse[static_cast<size_t>(r) * a.slice_max + i] - mx);   // exp(-inf) = 0: empty shard
-      const float2 v = *reinterpret_cast<const float2*>(rbuf + (static_cast<size_t>(r) * a.slice_max + i) * kHeadDim + 2 * lane);
+      const float w = __expf(__ldcg(rlse + static_cast<size_t>(r) * a.slice_max + i) - mx);   // exp(-inf) = 0: empty shard
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(rbuf + (static_cast<size_t>(r) * a.slice_max + i) * kHeadDim + 4 * lane));
       acc.x = fmaf(w, v.x, acc.x);
       acc.y = fmaf(w, v.y, acc.y);
+      acc.z = fmaf(w, v.z, acc.z);
+      acc.w = fmaf(w, v.w, acc.w);
       den += w;
     }
     const float inv = 1.f / den;
-    const __nv_bfloat162 o = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&lo);
+    o.y = *reinterpret_cast<const uint32_t*>(&hi);
     for (int p = 0; p < W; ++p)
-      *reinterpret_cast<__nv_bfloat162*>(a.out[p] + static_cast<size_t>(r0 + i) * kHeadDim + 2 * lane) = o;
+      *reinterpret_cast<uint2*>(a.out[p] + static_cast<size_t>(r0 + i) * kHeadDim + 4 * lane) = o;
   }
   __threadfence_system();
   __syncthreads();
@@ -194,7 +205,7 @@ int launch_kv_exchange(const float* parts, const float* lses, int splits, int ro
   GCT_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   GCT_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gct_kv_exchange_kernel, 256, 0));
   if (per_sm < 1) return fail(GCT_ERR_CUDA, "exchange: kernel does not fit on an SM");
-  const int grid = std::min(sms * std::min(per_sm, 2), (rows + 7) / 8);
+  const int grid = std::min(sms * std::min(per_sm, 4), (rows + 15) / 16);
   gct_kv_exchange_kernel<<<grid, 256, 0, stream>>>(a);
   GCT_CUDA_CHECK(cudaGetLastError());
   return GCT_OK;
