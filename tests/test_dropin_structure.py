@@ -146,6 +146,37 @@ def test_cpu_tensors_are_rejected_not_computed():
     q = torch.zeros(1, 4, 2, 64, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="no CPU path"):
         P.ops.dense_attention(q, q, q)
+    from lingbot_map_b200 import render_ops
+    pts = torch.zeros(8, 3)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        render_ops.frustum_cull(pts, torch.eye(3), torch.zeros(3), 1.0, 1.0, 0.0, 0.0, 4, 4, 0.1, 10.0)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        render_ops.voxelize_frame(pts, pts, 0.1)
+
+
+def test_camera_attention_keeps_reference_code_for_batch_mode():
+    """B200CausalAttention only takes over the streaming branch on a GPU; without a kv_cache (or on CPU tensors) the
+    call goes to the reference's own CausalAttention.forward.  Checked with a stand-in for that class."""
+    from lingbot_map_b200 import camera
+    seen = {}
+
+    class FakeReference:
+        @staticmethod
+        def forward(self, x, **kw):
+            seen.update(kw)
+            return x + 1
+
+    orig = camera._reference_causal_attention
+    camera._reference_causal_attention = lambda: FakeReference
+    try:
+        m = torch.nn.Module()
+        m.__class__ = camera.B200CausalAttention
+        m.head_dim = 128
+        x = torch.zeros(1, 3, 8)
+        assert torch.equal(m(x, kv_cache=None, global_idx=2), x + 1) and seen["global_idx"] == 2
+        assert torch.equal(m(x, kv_cache={"_skip_append": False}, num_frame_per_block=3), x + 1)   # CPU tensor
+    finally:
+        camera._reference_causal_attention = orig
 
 
 @pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lingbot_map")), reason="reference checkout not present")
@@ -171,7 +202,7 @@ def test_entry_scripts_compile_and_parse_their_arguments():
     import py_compile
     import subprocess
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    for name in ("bench.py", "__graft_entry__.py"):
+    for name in ("bench.py", "bench_model.py", "__graft_entry__.py"):
         py_compile.compile(os.path.join(root, name), doraise=True)
     r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--help"], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "--exact-softmax" in r.stdout and "--scale-frames" in r.stdout, r.stderr[-500:]
