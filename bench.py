@@ -391,7 +391,7 @@ def kvsplit_parity(hp, rank, dev):
     if rank == 0:
         for b in range(DEPTH):
             m.plan()                                            # the whole visible list
-            full = m.compute_attention.__func__(m, b, qs[b]) if b else m.compute_attention(0, qs[b])
+            full = m.compute_attention(b, qs[b])
             got = hp.outs[2 * b + 1].view(TPF, HEADS, HEAD_DIM)
             worst_abs = max(worst_abs, float((got.float() - full.float()).abs().max()))
             worst_cos = min(worst_cos, _cos64(got, full))
