@@ -304,14 +304,34 @@ def measure(hps, args, dev, rank, world, barrier, sampler, kvsplit):
 
     # ---- end to end: host buffers in, host buffers out, copies inside the timed region ----
     C3 = 3 * HEADS * HEAD_DIM
+    # KV-sharded stream: the frame's inputs are the same on every rank, so each rank moves only its 1/W slice of the
+    # rows over PCIe (host -> device, and of the results device -> host) and the ranks complete the inputs with an
+    # all-gather over NVLink on the copy stream; the bytes that cross PCIe per step are the same in total as for one GPU.
+    sliced = kvsplit and world > 1
+    rows_pad = -(-TPF // world) * world if sliced else TPF
+    sl = rows_pad // world if sliced else TPF
+    r_lo = rank * sl if sliced else 0
+    r_hi = min(r_lo + sl, TPF)
+
+    def host_slice(t):
+        full = torch.zeros(rows_pad, t.shape[1], dtype=t.dtype)
+        full[:TPF].copy_(t.cpu())
+        return full[r_lo:r_lo + sl].clone().pin_memory()
+
     e2e = []
     for hp in hps:
         st = {"hp": hp}
-        st["h_in_f"] = [t.cpu().pin_memory() for t in hp.qkv_frame]
-        st["h_in_g"] = [t.cpu().pin_memory() for t in hp.qkv_global]
-        st["h_out"] = [torch.empty(TPF, HEADS, HEAD_DIM, dtype=torch.bfloat16).pin_memory() for _ in range(2 * DEPTH)]
-        st["d_in_f"] = [torch.empty(TPF, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)]
-        st["d_in_g"] = [torch.empty(TPF, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)]
+        st["h_in_f"] = [host_slice(t) for t in hp.qkv_frame]
+        st["h_in_g"] = [host_slice(t) for t in hp.qkv_global]
+        st["h_out"] = [torch.empty(max(r_hi - r_lo, 0), HEADS, HEAD_DIM, dtype=torch.bfloat16).pin_memory()
+                       for _ in range(2 * DEPTH)]
+        st["d_buf_f"] = [torch.empty(rows_pad, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)]
+        st["d_buf_g"] = [torch.empty(rows_pad, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)]
+        st["d_in_f"] = [t[:TPF] for t in st["d_buf_f"]]
+        st["d_in_g"] = [t[:TPF] for t in st["d_buf_g"]]
+        if sliced:
+            st["d_sl_f"] = [torch.empty(sl, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)]
+            st["d_sl_g"] = [torch.empty(sl, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)]
         e2e.append(st)
     # Copies run on their own stream, one layer ahead of / behind the compute stream: the inputs of layer b
     # are uploaded while layer b-1 computes, and the outputs of layer b are downloaded while layer b+1
@@ -330,8 +350,14 @@ def measure(hps, args, dev, rank, world, barrier, sampler, kvsplit):
         def upload(b):
             with torch.cuda.stream(copy_stream):
                 copy_stream.wait_event(ev_free[b])
-                st["d_in_f"][b].copy_(st["h_in_f"][b], non_blocking=True)
-                st["d_in_g"][b].copy_(st["h_in_g"][b], non_blocking=True)
+                if sliced:
+                    st["d_sl_f"][b].copy_(st["h_in_f"][b], non_blocking=True)
+                    st["d_sl_g"][b].copy_(st["h_in_g"][b], non_blocking=True)
+                    dist.all_gather_into_tensor(st["d_buf_f"][b], st["d_sl_f"][b])
+                    dist.all_gather_into_tensor(st["d_buf_g"][b], st["d_sl_g"][b])
+                else:
+                    st["d_in_f"][b].copy_(st["h_in_f"][b], non_blocking=True)
+                    st["d_in_g"][b].copy_(st["h_in_g"][b], non_blocking=True)
                 ev_in[b].record(copy_stream)
 
         def before_layer(b):
@@ -348,7 +374,7 @@ def measure(hps, args, dev, rank, world, barrier, sampler, kvsplit):
                 copy_stream.wait_event(ev_out[b])
                 for i in (2 * b, 2 * b + 1):
                     hp.outs[i].record_stream(copy_stream)
-                    st["h_out"][i].copy_(hp.outs[i].view(TPF, HEADS, HEAD_DIM), non_blocking=True)
+                    st["h_out"][i].copy_(hp.outs[i].view(TPF, HEADS, HEAD_DIM)[r_lo:r_hi], non_blocking=True)
 
         def e2e_step():
             hp.step(st["d_in_f"], st["d_in_g"], before_layer, after_layer)
@@ -375,6 +401,7 @@ def measure(hps, args, dev, rank, world, barrier, sampler, kvsplit):
         "value": streams * args.steps / (total_ms / 1e3),
         "e2e_value": streams * args.e2e_steps / (e2e_ms / 1e3),
         "e2e_per_rank_fps": [len(hps) * args.e2e_steps / (x / 1e3) for x in per_rank],
+        # bytes that cross PCIe per step for one stream (a sharded stream moves them in W slices, one per rank)
         "h2d": 2 * DEPTH * TPF * C3 * 2, "d2h": 2 * DEPTH * TPF * HEADS * HEAD_DIM * 2,
     }
 

@@ -79,6 +79,7 @@ __global__ void __launch_bounds__(256) gct_kv_exchange_kernel(const ExchangeArgs
   const int R = a.rows, W = a.world;
   int* my_flags = a.flags[a.rank];
   int* counters = my_flags + 2 * W;
+  pdl_wait();      // the attention kernel's partials (and everything earlier in the stream) are complete from here on
 
   // ---- phase 1: my partial of every row goes to the rank that owns the row ----
   for (int row = ghalf; row < R; row += nhalves) {
@@ -206,8 +207,7 @@ int launch_kv_exchange(const float* parts, const float* lses, int splits, int ro
   GCT_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gct_kv_exchange_kernel, 256, 0));
   if (per_sm < 1) return fail(GCT_ERR_CUDA, "exchange: kernel does not fit on an SM");
   const int grid = std::min(sms * std::min(per_sm, 4), (rows + 15) / 16);
-  gct_kv_exchange_kernel<<<grid, 256, 0, stream>>>(a);
-  GCT_CUDA_CHECK(cudaGetLastError());
+  GCT_CUDA_CHECK(launch_pdl(gct_kv_exchange_kernel, dim3(grid), dim3(256), 0, stream, a));
   return GCT_OK;
 }
 
