@@ -131,10 +131,13 @@ class PeerExchange:
         _lib.check(lib.gct_kv_exchange_sizes(n_q, heads, self.world, C.byref(rb), C.byref(fb), C.byref(sl)))
         self.slice_rows = sl.value
         name = self.group.group_name
-        try:
-            symm.enable_symm_mem_for_group(name)
-        except Exception:                                    # not needed (and deprecated) in recent releases
-            pass
+        import warnings
+        with warnings.catch_warnings():                      # older releases need the call, recent ones deprecate it
+            warnings.simplefilter("ignore")
+            try:
+                symm.enable_symm_mem_for_group(name)
+            except Exception:                                # noqa: BLE001
+                pass
         self.recv = symm.empty(rb.value // 4, dtype=torch.float32, device=self.device)
         self.out = symm.empty(num_blocks * n_q * heads * 64, dtype=torch.bfloat16, device=self.device)
         self.flags = symm.empty(max(fb.value // 4, 64), dtype=torch.int32, device=self.device)
@@ -172,12 +175,20 @@ def make_exchange(manager, group=None) -> Optional[PeerExchange]:
     used then).  LINGBOT_B200_KV_EXCHANGE=allgather forces the fallback."""
     if os.environ.get("LINGBOT_B200_KV_EXCHANGE", "peer").lower() == "allgather":
         return None
+    xchg, err = None, None
     try:
-        return PeerExchange(manager.tokens_per_frame, manager.num_heads, manager.num_blocks, manager.device, group)
+        xchg = PeerExchange(manager.tokens_per_frame, manager.num_heads, manager.num_blocks, manager.device, group)
     except Exception as e:                                   # noqa: BLE001
-        import warnings
-        warnings.warn(f"peer exchange unavailable ({type(e).__name__}: {e}); using the NCCL all-gather path")
+        err = e
+    # every rank must take the same path: one rank without symmetric memory sends all of them to the all-gather
+    ok = torch.tensor([1 if xchg is not None else 0], dtype=torch.int32, device=manager.device)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+    if int(ok.item()) == 0:
+        if err is not None:
+            import warnings
+            warnings.warn(f"peer exchange unavailable ({type(err).__name__}: {err}); using the NCCL all-gather path")
         return None
+    return xchg
 
 
 def sharded_attention(manager, block_idx: int, q: torch.Tensor, rank: int, world: int, group=None,
