@@ -305,8 +305,11 @@ def measure(hps, args, dev, rank, world, barrier, sampler, kvsplit):
     # ---- end to end: host buffers in, host buffers out, copies inside the timed region ----
     C3 = 3 * HEADS * HEAD_DIM
     # KV-sharded stream: the frame's inputs are the same on every rank, so each rank moves only its 1/W slice of the
-    # rows over PCIe (host -> device, and of the results device -> host) and the ranks complete the inputs with an
-    # all-gather over NVLink on the copy stream; the bytes that cross PCIe per step are the same in total as for one GPU.
+    # rows over PCIe (host -> device, and of the results device -> host) and the ranks complete the inputs over NVLink:
+    # one coalesced all-gather of the step's 48 slices at the start of the step, on the compute stream (the per-layer
+    # exchange kernels wait on their peers and must not share the device with another kernel that does).  The slices
+    # of step s+1 are uploaded while step s computes (two slice sets).  The bytes that cross PCIe per step are the
+    # same in total as for one GPU.
     sliced = kvsplit and world > 1
     rows_pad = -(-TPF // world) * world if sliced else TPF
     sl = rows_pad // world if sliced else TPF
@@ -330,12 +333,12 @@ def measure(hps, args, dev, rank, world, barrier, sampler, kvsplit):
         st["d_in_f"] = [t[:TPF] for t in st["d_buf_f"]]
         st["d_in_g"] = [t[:TPF] for t in st["d_buf_g"]]
         if sliced:
-            st["d_sl_f"] = [torch.empty(sl, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)]
-            st["d_sl_g"] = [torch.empty(sl, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)]
+            st["d_sl_f"] = [[torch.empty(sl, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)] for _ in range(2)]
+            st["d_sl_g"] = [[torch.empty(sl, C3, dtype=torch.bfloat16, device=dev) for _ in range(DEPTH)] for _ in range(2)]
         e2e.append(st)
-    # Copies run on their own stream, one layer ahead of / behind the compute stream: the inputs of layer b
-    # are uploaded while layer b-1 computes, and the outputs of layer b are downloaded while layer b+1
-    # computes.  Events order every buffer hand-over in both directions.
+    # Copies run on their own stream.  Streams of independent frames: the inputs of layer b are uploaded while layer
+    # b-1 computes, and the outputs of layer b are downloaded while layer b+1 computes.  Events order every buffer
+    # hand-over in both directions.
     copy_stream = torch.cuda.Stream(device=dev)
     main_stream = torch.cuda.current_stream(dev)
 
@@ -350,14 +353,8 @@ def measure(hps, args, dev, rank, world, barrier, sampler, kvsplit):
         def upload(b):
             with torch.cuda.stream(copy_stream):
                 copy_stream.wait_event(ev_free[b])
-                if sliced:
-                    st["d_sl_f"][b].copy_(st["h_in_f"][b], non_blocking=True)
-                    st["d_sl_g"][b].copy_(st["h_in_g"][b], non_blocking=True)
-                    dist.all_gather_into_tensor(st["d_buf_f"][b], st["d_sl_f"][b])
-                    dist.all_gather_into_tensor(st["d_buf_g"][b], st["d_sl_g"][b])
-                else:
-                    st["d_in_f"][b].copy_(st["h_in_f"][b], non_blocking=True)
-                    st["d_in_g"][b].copy_(st["h_in_g"][b], non_blocking=True)
+                st["d_in_f"][b].copy_(st["h_in_f"][b], non_blocking=True)
+                st["d_in_g"][b].copy_(st["h_in_g"][b], non_blocking=True)
                 ev_in[b].record(copy_stream)
 
         def before_layer(b):
@@ -379,7 +376,48 @@ def measure(hps, args, dev, rank, world, barrier, sampler, kvsplit):
         def e2e_step():
             hp.step(st["d_in_f"], st["d_in_g"], before_layer, after_layer)
             main_stream.wait_stream(copy_stream)                 # the step ends when its results are on the host
-        return e2e_step
+
+        if not sliced:
+            return e2e_step
+
+        ev_sl_in = [torch.cuda.Event() for _ in range(2)]        # slice set s of the next step is on the device
+        ev_sl_free = [torch.cuda.Event() for _ in range(2)]      # the all-gather has read slice set s
+        for e in ev_sl_free:
+            e.record(main_stream)
+        state = {"set": 0, "primed": False}
+
+        def upload_slices(s):
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(ev_sl_free[s])
+                for b in range(DEPTH):
+                    st["d_sl_f"][s][b].copy_(st["h_in_f"][b], non_blocking=True)
+                    st["d_sl_g"][s][b].copy_(st["h_in_g"][b], non_blocking=True)
+                ev_sl_in[s].record(copy_stream)
+
+        def after_layer_sliced(b):
+            ev_out[b].record(main_stream)
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(ev_out[b])
+                for i in (2 * b, 2 * b + 1):
+                    hp.outs[i].record_stream(copy_stream)
+                    st["h_out"][i].copy_(hp.outs[i].view(TPF, HEADS, HEAD_DIM)[r_lo:r_hi], non_blocking=True)
+
+        def e2e_step_sliced():
+            s = state["set"]
+            if not state["primed"]:
+                upload_slices(s)
+                state["primed"] = True
+            main_stream.wait_event(ev_sl_in[s])
+            with dist._coalescing_manager():
+                for b in range(DEPTH):
+                    dist.all_gather_into_tensor(st["d_buf_f"][b], st["d_sl_f"][s][b])
+                    dist.all_gather_into_tensor(st["d_buf_g"][b], st["d_sl_g"][s][b])
+            ev_sl_free[s].record(main_stream)
+            upload_slices(1 - s)                                 # the next step's slices cross PCIe under this step
+            state["set"] = 1 - s
+            hp.step(st["d_in_f"], st["d_in_g"], None, after_layer_sliced)
+            main_stream.wait_stream(copy_stream)                 # the step ends when its result slices are on the host
+        return e2e_step_sliced
 
     e2e_steps = [make_e2e_step(st) for st in e2e]
 

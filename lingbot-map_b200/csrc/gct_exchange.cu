@@ -42,35 +42,56 @@ struct ExchangeArgs {
   int* status;
 };
 
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// Flag traffic is relaxed at system scope; ordering comes from one system-scope fence before a batch of flag stores
+// and one after a batch of flag polls (a release store or an acquire load per flag would pay a fence each, `world`
+// times in a row).
+__device__ __forceinline__ void st_relaxed_sys(int* p, int v) {
+  asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+__device__ __forceinline__ int ld_relaxed_sys(const int* p) {
   int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
 
-// Wait until all `world` flags at `f` have reached `epoch`.  One thread polls; returns false on a timeout.
+// Wait until all `world` flags at `f` have reached `epoch`, then fence (acquire side).  One thread polls, all flags
+// per round (independent loads, one round trip); returns false on a timeout.
 __device__ bool wait_flags(const int* f, int world, int epoch, int* status) {
   const long long t0 = clock64();
-  for (int r = 0; r < world; ++r) {
-    unsigned it = 0;
-    while (ld_acquire_sys(f + r) - epoch < 0) {      // epochs only grow; the difference handles wrap-around
-      if ((++it & 255u) == 0u) {
-        if (clock64() - t0 > kXchgWaitCycles || *reinterpret_cast<volatile int*>(status) != 0) {
-          atomicCAS(status, 0, kStatusWaitTimeout);
-          return false;
-        }
-        __nanosleep(100);
+  for (unsigned it = 1;; ++it) {
+    int behind = 0;
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r)
+      if (r < world) behind |= (ld_relaxed_sys(f + r) - epoch) >> 31;   // epochs only grow; the difference handles wrap-around
+    if (behind == 0) break;
+    if ((it & 255u) == 0u) {
+      if (clock64() - t0 > kXchgWaitCycles || *reinterpret_cast<volatile int*>(status) != 0) {
+        atomicCAS(status, 0, kStatusWaitTimeout);
+        return false;
       }
+      __nanosleep(100);
     }
   }
+  __threadfence_system();
   return true;
 }
 
+// Called by one thread of every CTA after the CTA's barrier: counts the CTA in; the last one to arrive publishes
+// `epoch` in slot `rank` of every peer's flag row.  The fence before the count makes this CTA's stores (its other
+// threads' stores reached this thread through the barrier) visible at system scope before the count can be seen,
+// the fences around the publication chain that to the flag stores.
+__device__ void count_in_and_publish(int* counter, int* const* flags, int slot, int world, int epoch) {
+  __threadfence_system();
+  const int prev = atomicAdd(counter, 1);
+  if (prev == static_cast<int>(gridDim.x) - 1) {
+    *counter = 0;
+    __threadfence_system();
+    for (int p = 0; p < world; ++p) st_relaxed_sys(flags[p] + slot, epoch);
+  }
+}
+
 // A half-warp per row: 16 lanes x float4 = the 64 output elements; two rows per warp are in flight at once.
-__global__ void __launch_bounds__(256) gct_kv_exchange_kernel(const ExchangeArgs a) {
+__global__ void __launch_bounds__(256, 4) gct_kv_exchange_kernel(const ExchangeArgs a) {
   __shared__ int s_flag;
   const int lane = threadIdx.x & 15;
   const int halves_per_cta = blockDim.x >> 4;
@@ -116,16 +137,10 @@ __global__ void __launch_bounds__(256) gct_kv_exchange_kernel(const ExchangeArgs
     *reinterpret_cast<float4*>(rbuf + slot * kHeadDim + 4 * lane) = acc;
     if (lane == 0) rbuf[static_cast<size_t>(W) * a.slice_max * kHeadDim + slot] = lse;
   }
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
     // the last CTA to get here publishes: everything this rank sent is visible before the flag
-    const int prev = atomicAdd(counters + 0, 1);
-    if (prev == static_cast<int>(gridDim.x) - 1) {
-      counters[0] = 0;
-      __threadfence_system();
-      for (int p = 0; p < W; ++p) st_release_sys(a.flags[p] + a.rank, a.epoch);
-    }
+    count_in_and_publish(counters + 0, a.flags, a.rank, W, a.epoch);
     s_flag = wait_flags(my_flags, W, a.epoch, a.status) ? 1 : 0;
   }
   __syncthreads();
@@ -137,18 +152,32 @@ __global__ void __launch_bounds__(256) gct_kv_exchange_kernel(const ExchangeArgs
   const float* rbuf = a.recv[a.rank];
   const float* rlse = rbuf + static_cast<size_t>(W) * a.slice_max * kHeadDim;
   for (int i = ghalf; i < r1 - r0; i += nhalves) {
+    // independent loads first (one round trip per batch), then the arithmetic
+    float ls[kMaxWorld];
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r) ls[r] = (r < W) ? __ldcg(rlse + static_cast<size_t>(r) * a.slice_max + i) : -INFINITY;
     float mx = -INFINITY;
-    for (int r = 0; r < W; ++r) mx = fmaxf(mx, __ldcg(rlse + static_cast<size_t>(r) * a.slice_max + i));
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r) mx = fmaxf(mx, ls[r]);
     float den = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = 0; r < W; ++r) {
-      const float w = __expf(__ldcg(rlse + static_cast<size_t>(r) * a.slice_max + i) - mx);   // exp(-inf) = 0: empty shard
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(rbuf + (static_cast<size_t>(r) * a.slice_max + i) * kHeadDim + 4 * lane));
-      acc.x = fmaf(w, v.x, acc.x);
-      acc.y = fmaf(w, v.y, acc.y);
-      acc.z = fmaf(w, v.z, acc.z);
-      acc.w = fmaf(w, v.w, acc.w);
-      den += w;
+#pragma unroll
+    for (int base = 0; base < kMaxWorld; base += 8) {
+      if (base >= W) break;
+      float4 v[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        v[r] = (base + r < W) ? __ldcg(reinterpret_cast<const float4*>(rbuf + (static_cast<size_t>(base + r) * a.slice_max + i) * kHeadDim + 4 * lane))
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float w = (base + r < W) ? __expf(ls[base + r] - mx) : 0.f;   // exp(-inf) = 0: empty shard
+        acc.x = fmaf(w, v[r].x, acc.x);
+        acc.y = fmaf(w, v[r].y, acc.y);
+        acc.z = fmaf(w, v[r].z, acc.z);
+        acc.w = fmaf(w, v[r].w, acc.w);
+        den += w;
+      }
     }
     const float inv = 1.f / den;
     const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
@@ -158,17 +187,12 @@ __global__ void __launch_bounds__(256) gct_kv_exchange_kernel(const ExchangeArgs
     for (int p = 0; p < W; ++p)
       *reinterpret_cast<uint2*>(a.out[p] + static_cast<size_t>(r0 + i) * kHeadDim + 4 * lane) = o;
   }
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
-    const int prev = atomicAdd(counters + 1, 1);
-    if (prev == static_cast<int>(gridDim.x) - 1) {
-      counters[1] = 0;
-      __threadfence_system();
-      for (int p = 0; p < W; ++p) st_release_sys(a.flags[p] + W + a.rank, a.epoch);
-      // the kernel ends on this rank only when every rank's slice has landed here
-      wait_flags(my_flags + W, W, a.epoch, a.status);
-    }
+    count_in_and_publish(counters + 1, a.flags, W + a.rank, W, a.epoch);
+    // the kernel ends on this rank only when every rank's slice has landed here (one CTA waits; a grid ends when
+    // all of its CTAs have)
+    if (blockIdx.x == 0) wait_flags(my_flags + W, W, a.epoch, a.status);
   }
 }
 
