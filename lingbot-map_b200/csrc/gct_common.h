@@ -76,6 +76,8 @@ struct AttnLaunch {
   int n_q = 0, heads = 0, batch = 1;
   int q_tiles_per_cta = 2;           // 1 or 2
   int splits = 1;
+  int split_len = 0;                 // 0: `splits` equal ranges of KV blocks; > 0: splits - 1 ranges of split_len blocks, the last
+                                     // one takes the (shorter) rest and its CTAs are launched last
   bool final_bf16 = true;            // true: write bf16 out (requires splits == 1); false: partials
   __nv_bfloat16* out = nullptr;      // [batch, n_q, H, 64]
   float* part_o = nullptr;           // [splits, batch, n_q, H, 64] normalised partial outputs
@@ -96,9 +98,11 @@ int make_tensor_map(CUtensorMap* out, const void* base, int heads, int64_t token
                     int64_t head_stride, int64_t token_stride, int64_t page_stride);
 
 // Pick (q_tiles_per_cta, splits) for a problem: n_q_tiles query tiles of 128 rows per (head,batch),
-// total_blocks KV blocks, on num_sms SMs, with at most max_splits partial results.
+// total_blocks KV blocks, on num_sms SMs, with at most max_splits partial results.  With split_len != nullptr the
+// plan may also be splits - 1 long ranges plus one short one (AttnLaunch::split_len), which fills the SMs that a whole
+// number of equal ranges leaves idle; *split_len = 0 when equal ranges are at least as good.
 void choose_attention_config(int n_q_tiles, int heads_x_batch, int total_blocks, int num_sms, int max_splits,
-                             int* q_tiles_per_cta, int* splits);
+                             int* q_tiles_per_cta, int* splits, int* split_len = nullptr);
 
 // ---- elementwise kernels ---------------------------------------------------------------
 struct PrepLaunch {

@@ -679,7 +679,8 @@ static int run_paged(gct_mgr* m, int block, const void* q_dev, int q_dtype, int 
   int sms = 148;
   rc = device_sm_count(&sms);
   if (rc != GCT_OK) return rc;
-  choose_attention_config((n_q + kTileM - 1) / kTileM, H, total_blocks, sms, m->max_splits, &a.q_tiles_per_cta, &a.splits);
+  choose_attention_config((n_q + kTileM - 1) / kTileM, H, total_blocks, sms, m->max_splits, &a.q_tiles_per_cta, &a.splits,
+                          &a.split_len);
   const int64_t rows = static_cast<int64_t>(n_q) * H;
   // Bounded mode: every key of this block's cache went through the manager, so |q_row| * max|k| bounds the row's
   // logits; while that bound stays small it replaces the running row maximum (decided per CTA inside the kernel).

@@ -565,6 +565,30 @@ def test_headline_kv_every_row_of_two_heads(headline_cache, mode):
     assert m.device_status() == 0
 
 
+@pytest.mark.parametrize("pages", [(0, 17), (33, 67), (116, 133)])
+def test_page_slices_of_the_headline_cache(headline_cache, pages):
+    """What one rank of a KV-sharded stream computes: attention over a slice of the visible page list (17 or 34 pages
+    of the 133: 136 / 272 KV blocks, where the launch uses long KV ranges plus one short range per head and query
+    group instead of equal ranges; the last slice ends with the partly filled special page).  All rows of one head,
+    output and log-sum-exp, against the float64 oracle over the same tokens."""
+    m, q, _ = headline_cache
+    lo, hi = pages
+    kk, vv = m._gather_kv(0)
+    t0, t1 = lo * 999, min(hi * 999, kk.shape[0])
+    h = 7
+    wo, wl = O.attention(q[:, h:h + 1].float().cpu().numpy().astype(np.float64),
+                         kk[t0:t1, h:h + 1].float().cpu().numpy().astype(np.float64),
+                         vv[t0:t1, h:h + 1].float().cpu().numpy().astype(np.float64))
+    try:
+        m.plan(lo, hi)
+        out, lse = m.compute_attention_partial(0, q)
+    finally:
+        m.plan()
+    assert_close(out[:, h:h + 1], wo, f"pages [{lo}, {hi})")
+    assert np.abs(lse[:, h].cpu().numpy() - wl[:, 0]).max() < 4e-3      # bounded mode: see the test above
+    assert m.device_status() == 0
+
+
 def test_bounded_mode_is_chosen_per_cta(headline_cache):
     """Two query rows (in different query tiles) get a norm that makes their Cauchy-Schwarz bound too loose: only the
     CTAs that hold them fall back to the running maximum, inside the same launch; every row still matches the oracle
