@@ -214,7 +214,10 @@ int gct_lse_merge_strided(const float* parts_dev, const float* lse_dev, int grou
  *   recv_ptrs[r], out_ptrs[r], flag_ptrs[r]: rank r's receive buffer (gct_kv_exchange_sizes bytes), output
  *   [n_q, H, 64] bf16 and flag words (zeroed once before the first call), as addresses valid on THIS device
  *   (symmetric / peer-mapped memory; entry `rank` is local memory).  epoch: 1, 2, 3, ... per call on the same flag
- *   words, identical on every rank.  All waits are bounded; a timeout sets the manager's device status word. */
+ *   words, identical on every rank.  All waits are bounded; a timeout sets the manager's device status word.
+ *   The exchange kernel's CTAs wait on their peers and its grid is sized to be resident at once on an otherwise
+ *   idle device: do not run another kernel that itself waits on a peer (a collective on a second stream, say)
+ *   beside it - each could keep the other's CTAs from being scheduled until the bounded waits give up. */
 int gct_kv_exchange_sizes(int n_q, int heads, int world, size_t* recv_bytes_out, size_t* flag_bytes_out,
                           int* slice_rows_out);
 int gct_mgr_attention_exchange(gct_mgr_t* m, int block, const void* q_dev, int q_dtype, int n_q, int rank, int world,

@@ -7,11 +7,15 @@
 //
 // One kernel per layer and rank, two phases, plain loads and stores on peer-mapped addresses over NVLink:
 //   phase 1  for every peer p: merge my S local partials of the rows in p's row slice and store the record
-//            [O(64) | lse] into slot `rank` of p's receive buffer; then raise flag1[rank] on every peer.
+//            [O(64) | lse] into slot `rank` of p's receive buffer; the last CTA to finish raises flag1[rank] on every
+//            peer.
 //   phase 2  wait until flag1[r] of every rank r has reached this call's epoch; merge the W records of MY row slice
-//            (log-sum-exp weights), round to bf16 and store the rows into every rank's output buffer; raise
-//            flag2[rank] on every peer; the CTA that raised it waits for all flag2, so that the kernel's end on a
+//            (log-sum-exp weights), round to bf16 and store the rows into every rank's output buffer; the last CTA to
+//            finish raises flag2[rank] on every peer and CTA 0 waits for all flag2, so that the kernel's end on a
 //            stream means the whole output has landed locally.
+// Ordering: data stores -> CTA barrier -> one thread's system-scope fence -> CTA counter -> (last CTA) fence ->
+// relaxed system-scope flag stores; on the other side relaxed polls of all flags, then one fence, then the CTA
+// barrier.  One fence per batch of flags instead of a release / acquire per flag.
 // Row slices are contiguous: rank r owns rows [r*R/W, (r+1)*R/W).  Each rank sends (W-1)/W of one record and one
 // bf16 slice per peer instead of a whole record to everybody.
 // Flags are epoch counters (monotonic per exchange object), never reset.  Every wait is bounded: on a timeout the
