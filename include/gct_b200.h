@@ -165,6 +165,14 @@ int gct_mgr_kernel_time(gct_mgr_t* m, double* total_ms_out, int* launches_out);
 /* Number of kernels this manager has launched since creation. */
 int gct_mgr_launch_count(const gct_mgr_t* m, int64_t* count_out);
 
+/* How a paged attention call of the manager is cut into CTAs (host arithmetic only, no device needed; the reference
+ * leaves this to FlashInfer's plan(), flashinfer_cache.py:398-410): n_q query rows, `heads` heads, kv_blocks KV
+ * blocks of 128 tokens, on a device with num_sms SMs, at most max_splits partial results per row.  Outputs: query
+ * tiles of 128 rows per CTA (1 or 2), the number of KV ranges per (head, query group), and split_len: 0 = equal
+ * ranges, > 0 = splits - 1 ranges of split_len blocks followed by one shorter range whose CTAs are launched last. */
+int gct_attn_launch_shape(int n_q, int heads, int kv_blocks, int num_sms, int max_splits, int* q_tiles_per_cta_out,
+                          int* splits_out, int* split_len_out);
+
 /* ---- stand-alone operators --------------------------------------------------------- */
 
 /* Dense non-causal attention, the F.scaled_dot_product_attention call of Attention.forward

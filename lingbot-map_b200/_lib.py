@@ -64,6 +64,7 @@ SIGNATURES = {
     "gct_mgr_launch_count": (_i, [_vp, _pi64]),
     "gct_mgr_kernel_timing": (_i, [_vp, _i]),
     "gct_mgr_kernel_time": (_i, [_vp, C.POINTER(C.c_double), _pi]),
+    "gct_attn_launch_shape": (_i, [_i, _i, _i, _i, _i, _pi, _pi, _pi]),
     "gct_attn_dense": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _pi64, _pi64, _pi64, _vp, _sz, _vp]),
     "gct_prep_qkv": (_i, [_vp, _i, _i64, _i, _i, _i, _pf, _pf, _pf, _pf, _pf, _i, _vp, _vp, _vp, _vp]),
     "gct_rope3d_table": (_i, [_i, _i, _i, _i, _vp, _vp]),

@@ -776,6 +776,16 @@ int gct_mgr_launch_count(const gct_mgr_t* m, int64_t* count_out) {
 
 // ---- stand-alone operators ---------------------------------------------------------------
 
+int gct_attn_launch_shape(int n_q, int heads, int kv_blocks, int num_sms, int max_splits, int* q_tiles_per_cta_out,
+                          int* splits_out, int* split_len_out) {
+  if (n_q <= 0 || heads <= 0 || kv_blocks <= 0 || num_sms <= 0 || max_splits <= 0 || q_tiles_per_cta_out == nullptr ||
+      splits_out == nullptr || split_len_out == nullptr)
+    return fail(GCT_ERR_INVALID, "gct_attn_launch_shape: bad argument");
+  choose_attention_config((n_q + kTileM - 1) / kTileM, heads, kv_blocks, num_sms, max_splits, q_tiles_per_cta_out, splits_out,
+                          split_len_out);
+  return GCT_OK;
+}
+
 int gct_attn_dense(const void* q_dev, const void* k_dev, const void* v_dev, void* out_dev, int batch, int n_q, int n_kv,
                    int heads, const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
                    void* workspace_dev, size_t workspace_bytes, void* stream) {

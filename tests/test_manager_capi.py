@@ -137,3 +137,36 @@ def test_compute_needs_device():
         P.B200KVCacheManager(1, 21, 26, 1, 64, force_fp32=True, bookkeeping_only=True)
     with pytest.raises(RuntimeError, match="CUDA tensor"):
         P.ops.dense_attention(*(torch.zeros(1, 4, 1, 64, dtype=torch.bfloat16) for _ in range(3)))
+
+
+def test_launch_shape_covers_the_kv_blocks():
+    """Host arithmetic of the paged attention launch: every plan covers the KV blocks exactly once with non-empty
+    ranges; equal ranges at the benchmark's size, long ranges plus a short one where equal ranges would leave SMs idle
+    (one rank's slice of a stream sharded over 4 or 8 GPUs)."""
+    import ctypes as C
+    lib = _lib.load()
+
+    def shape(n_q, heads, blocks, sms=148, max_splits=16):
+        qt, s, ln = C.c_int(), C.c_int(), C.c_int()
+        _lib.check(lib.gct_attn_launch_shape(n_q, heads, blocks, sms, max_splits, C.byref(qt), C.byref(s), C.byref(ln)))
+        return qt.value, s.value, ln.value
+
+    for n_q in (1, 6, 130, 1005, 8040):
+        for heads in (1, 2, 16, 48):
+            for blocks in (1, 2, 7, 8, 64, 128, 136, 264, 272, 529, 673, 1057, 1100):
+                for max_splits in (1, 4, 16):
+                    qt, s, ln = shape(n_q, heads, blocks, max_splits=max_splits)
+                    assert qt in (1, 2) and 1 <= s <= min(blocks, max_splits)
+                    if ln:
+                        rest = blocks - (s - 1) * ln
+                        assert s >= 2 and 1 <= rest <= ln
+                    else:
+                        assert all((i + 1) * blocks // s > i * blocks // s for i in range(s))
+    assert shape(1005, 16, 1057) == (2, 9, 0)                     # the 10,000-frame cache on one GPU
+    qt, s, ln = shape(1005, 16, 136)                              # 17 of its 133 pages
+    assert (qt, s) == (2, 3) and 0 < 136 - 2 * ln < ln
+    qt, s, ln = shape(1005, 16, 272)                              # 34 pages
+    assert (qt, s) == (2, 3) and 0 < 272 - 2 * ln < ln
+    assert shape(1005, 16, 136) == shape(1005, 16, 136)           # the cached plan equals the computed one
+    with pytest.raises(Exception):
+        _lib.check(lib.gct_attn_launch_shape(0, 16, 8, 148, 16, C.byref(C.c_int()), C.byref(C.c_int()), C.byref(C.c_int())))
