@@ -315,7 +315,7 @@ constexpr int kMaxChains = GCT_MAX_CHAINS;
 #define GCT_BOUNDED_POLY_DEG 3
 #endif
 #ifndef GCT_BOUNDED_HALF_AT
-#define GCT_BOUNDED_HALF_AT 28
+#define GCT_BOUNDED_HALF_AT 30
 #endif
 constexpr int kBoundedPolyNum = GCT_BOUNDED_POLY_NUM, kBoundedPolyDen = GCT_BOUNDED_POLY_DEN;
 constexpr int kBoundedPolyDeg = GCT_BOUNDED_POLY_DEG;
