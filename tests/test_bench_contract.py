@@ -44,3 +44,16 @@ def test_gpu_arm_has_no_cpu_path():
     assert p.returncode != 0
     assert "CUDA device" in (p.stderr + p.stdout)
     assert not any(ln.lstrip().startswith("{") for ln in p.stdout.splitlines())
+
+
+def test_reference_arm_under_torchrun_prints_on_rank_0_only():
+    env = dict(os.environ)
+    p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29541", os.path.join(ROOT, "bench.py"),
+                        "--impl", "reference", "--gpus", "2", "--frames-cached", "80", "--steps", "1", "--warmup", "0"],
+                       cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [ln for ln in p.stdout.splitlines() if ln.lstrip().startswith("{")]
+    assert len(lines) == 1, p.stdout
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["n_gpus"] == 2 and d["value"] > 0
