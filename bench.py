@@ -29,6 +29,7 @@ At N = 1 the line also carries, measured after and outside the timed regions:
                     reference's FlashInfer backend (bench_model.py, one subprocess each).
 """
 import argparse
+import contextlib
 import json
 import os
 import statistics
@@ -408,7 +409,8 @@ def measure(hps, args, dev, rank, world, barrier, sampler, kvsplit):
                 upload_slices(s)
                 state["primed"] = True
             main_stream.wait_event(ev_sl_in[s])
-            with dist._coalescing_manager():
+            # one launch for the 48 gathers where the installed torch can coalesce them, else one launch each
+            with getattr(dist, "_coalescing_manager", contextlib.nullcontext)():
                 for b in range(DEPTH):
                     dist.all_gather_into_tensor(st["d_buf_f"][b], st["d_sl_f"][s][b])
                     dist.all_gather_into_tensor(st["d_buf_g"][b], st["d_sl_g"][s][b])
