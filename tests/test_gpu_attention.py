@@ -670,3 +670,44 @@ def test_exchange_kernel_with_one_rank_equals_single_pass():
             assert_close(out, O.attention(r(q), kk, vv)[0], f"exchange world=1 epoch {epoch} ({tpf}x{H})")
             assert flags[:2].tolist() == [epoch, epoch] and flags[2:4].tolist() == [0, 0]
         assert m.device_status() == 0
+
+
+def test_exchange_wait_runs_out_when_a_peer_never_signals():
+    """The exchange kernel's waits are bounded: with world = 2 and nobody playing rank 1 (its buffers are plain local
+    tensors that nothing ever flags) the kernel gives up after about two seconds, records the time-out in the status
+    word and returns; the host reads it as an error, and the device goes on working."""
+    import ctypes as C
+    import time
+    from lingbot_map_b200.cache import _stream_ptr
+    lib = _lib.load()
+    tpf, H = 134, 2
+    m = P.B200KVCacheManager(1, 24, tpf, H, 64, device=DEV, scale_frames=2, sliding_window=4, max_total_frames=64)
+    for t in range(3):
+        m.append_frame(0, bf(seeded.randn(900 + t, tpf, H, 64)), bf(seeded.randn(950 + t, tpf, H, 64)))
+        m.evict_frames(0, 2, 4)
+    rb, fb, sl = C.c_size_t(), C.c_size_t(), C.c_int()
+    _lib.check(lib.gct_kv_exchange_sizes(tpf, H, 2, C.byref(rb), C.byref(fb), C.byref(sl)))
+    recv = [torch.zeros(rb.value // 4, dtype=torch.float32, device=DEV) for _ in range(2)]
+    flags = [torch.zeros(64, dtype=torch.int32, device=DEV) for _ in range(2)]
+    out = [torch.zeros(tpf, H, 64, dtype=torch.bfloat16, device=DEV) for _ in range(2)]
+    two = lambda ts: (C.c_void_p * 2)(*[t.data_ptr() for t in ts])
+    m.plan()
+    qd = bf(seeded.randn(990, tpf, H, 64))
+    t0 = time.perf_counter()
+    _lib.check(lib.gct_mgr_attention_exchange(m._handle, 0, qd.data_ptr(), _lib.BF16, tpf, 0, 2, 1, two(recv), two(out),
+                                              two(flags), sl.value, 1, _stream_ptr(m.device)))
+    with pytest.raises(Exception, match="device status"):
+        m.device_status()
+    waited = time.perf_counter() - t0
+    assert 0.5 < waited < 20.0, waited
+    assert flags[0][:2].tolist() == [1, 0] and flags[1][0].item() == 1     # rank 0 published, rank 1 never did
+    assert float(out[0].float().abs().max()) == 0.0                          # nothing was merged or stored
+    # the context is intact: a fresh manager (its own status word) computes as usual
+    m2 = P.B200KVCacheManager(1, 24, tpf, H, 64, device=DEV, scale_frames=2, sliding_window=4, max_total_frames=64)
+    orc = O.PagedCacheOracle(1, tpf, H, 64, scale_frames=2, sliding_window=4, max_total_frames=64)
+    k, v = seeded.randn(901, tpf, H, 64), seeded.randn(951, tpf, H, 64)
+    m2.append_frame(0, bf(k), bf(v))
+    orc.append_frame(0, r(k), r(v))
+    q = seeded.randn(991, tpf, H, 64)
+    assert_close(m2.compute_attention(0, bf(q)), orc.compute_attention(0, r(q)), "after a timed-out exchange")
+    assert m2.device_status() == 0
